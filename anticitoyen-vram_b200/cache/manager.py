@@ -6,7 +6,10 @@ What a mixer keeps for a request is declared as a *need*:
 * ``PagedNeed``  - something that grows by one entry for each token (attention's
   keys and values), kept in pages of ``page_size`` tokens; with ``window`` > 0
   only the last ``window`` tokens are ever read again, so older pages go back to
-  the pool as soon as the window has passed them.
+  the pool as soon as the window has passed them; with ``chunk`` > 0 a token
+  reads only the tokens of its own chunk of ``chunk`` positions (counted from
+  position 0), so the pages before the chunk of the next token go back.  A key
+  row (``head_dim`` elements) and a value row (``value_dim``) may differ in size.
 * ``StateNeed``  - a tensor of fixed shape for each live request (a recurrent
   state), kept in a slot that is given at admission, zeroed, and taken back when
   the request ends.
@@ -66,18 +69,46 @@ class CacheAccountingError(AssertionError):
 @dataclass(frozen=True)
 class PagedNeed:
     num_kv_heads: int
-    head_dim: int
+    head_dim: int           # elements of a key row of one kv-head
     window: int = 0
+    value_dim: int = 0      # elements of a value row; 0: as many as a key row
+    chunk: int = 0
 
     @property
     def kind(self) -> str:
         return "paged"
 
     @property
+    def value_size(self) -> int:
+        return self.value_dim or self.head_dim
+
+    @property
+    def keeps_all(self) -> bool:
+        return self.window <= 0 and self.chunk <= 0
+
+    @property
     def takes_over(self) -> bool:
         """Whether a new request can start on pages that an earlier request filled: yes where all keys are kept
-        (a window gives pages back as it goes, so an earlier request's first pages are gone)."""
-        return self.window <= 0
+        (a window or a chunked mask gives pages back as it goes, so an earlier request's first pages are gone)."""
+        return self.keeps_all
+
+    def first_needed(self, kv_len: int) -> int:
+        """The first position that a query at position ``kv_len`` or later can still read."""
+        lo = 0
+        if self.window > 0:
+            lo = max(lo, kv_len - self.window + 1)
+        if self.chunk > 0:
+            lo = max(lo, kv_len // self.chunk * self.chunk)
+        return lo
+
+    def widened(self, other: "PagedNeed") -> "PagedNeed":
+        """The need of a cache slot that mixers with this need and with ``other`` both read: rows of the same
+        sizes, and whatever either of them may read again is kept (different rules of forgetting: everything)."""
+        if (self.num_kv_heads, self.head_dim, self.value_size) != (other.num_kv_heads, other.head_dim, other.value_size):
+            raise ValueError(f"{self} and {other} cannot share a cache slot: their rows differ")
+        if (self.window, self.chunk) == (other.window, other.chunk):
+            return self
+        return PagedNeed(self.num_kv_heads, self.head_dim, 0, self.value_dim, 0)
 
 
 @dataclass(frozen=True)
@@ -228,12 +259,11 @@ class PagedGroup:
         table.extend(pages)
 
     def trim(self, request, kv_len: int) -> int:
-        """Give back the pages whose every key is out of the window of any later query."""
-        w = self.need.window
-        if w <= 0:
+        """Give back the pages whose every key is out of the window (or before the chunk) of any later query."""
+        if self.need.keeps_all:
             return 0
         table = self.tables[request]
-        releasable = max(0, (kv_len - w + 1) // self.page_size)
+        releasable = max(0, self.need.first_needed(kv_len) // self.page_size)
         releasable = min(releasable, len(table))
         start = self.first_live[request]
         freed = [table[i] for i in range(start, releasable)]
@@ -427,7 +457,7 @@ class CacheManager:
         """Could a request of ``length`` tokens ever be held, with every page free?
 
         A windowed group frees pages as it goes, but within one step it may need the whole portion."""
-        return all(g.pages_for(length) <= g.pool.num_pages for g in self.paged_groups if g.need.window <= 0)
+        return all(g.pages_for(length) <= g.pool.num_pages for g in self.paged_groups if g.need.keeps_all)
 
     def free_pages(self) -> list[int]:
         return [g.pool.num_free for g in self.paged_groups]

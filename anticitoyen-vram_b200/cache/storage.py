@@ -12,7 +12,9 @@ class CacheStorage:
 
     Paged group: ``[slots, 2, num_pages, kv_heads, page_size, head_dim]`` (keys at
     index 0 of the second axis, values at 1); a page of one kv-head is contiguous,
-    so a tile of keys is a run of ``page_size * head_dim`` elements.  The
+    so a tile of keys is a run of ``page_size * head_dim`` elements.  Where a value
+    row has another size than a key row, keys and values are two tensors,
+    ``[slots, num_pages, kv_heads, page_size, head_dim]`` and ``[..., value_dim]``.  The
     reference keeps ``[num_blocks, 16, kv_heads, head_dim]`` per layer
     (acvram/memory/kvcache.py:463-469).  State group:
     ``[slots, max_requests + 1, *shape]`` (the last slot belongs to nobody: padding rows of a
@@ -28,14 +30,21 @@ class CacheStorage:
         self.device = torch.device(device)
         self.dtype = dtype
         self.tensors: list[torch.Tensor] = []
+        self.value_tensors: dict[int, torch.Tensor] = {}    # group index -> values, where their rows differ from the keys'
         self.tables: dict[int, torch.Tensor] = {}       # group index -> the group's block table on the device
         for gi, g in enumerate(manager.groups):
             if isinstance(g, PagedGroup):
-                shape = (g.num_slots, 2, max(g.pool.num_pages, 1), g.need.num_kv_heads, g.page_size, g.need.head_dim)
-                self.tensors.append(torch.zeros(shape, device=self.device, dtype=dtype))
+                pages = max(g.pool.num_pages, 1)
+                if g.need.value_size == g.need.head_dim:
+                    shape = (g.num_slots, 2, pages, g.need.num_kv_heads, g.page_size, g.need.head_dim)
+                    self.tensors.append(torch.zeros(shape, device=self.device, dtype=dtype))
+                else:
+                    shape = (g.num_slots, pages, g.need.num_kv_heads, g.page_size)
+                    self.tensors.append(torch.zeros((*shape, g.need.head_dim), device=self.device, dtype=dtype))
+                    self.value_tensors[gi] = torch.zeros((*shape, g.need.value_size), device=self.device, dtype=dtype)
                 # a request that keeps all its keys can never hold more pages than the pool has
                 tokens = max_len if max_len else g.pool.num_pages * g.page_size
-                if g.need.window <= 0:
+                if g.need.keeps_all:
                     tokens = min(tokens, g.pool.num_pages * g.page_size)
                 width = max(1, g.pages_for(tokens))
                 self.tables[gi] = torch.full((manager.max_requests + 1, width), -1, device=self.device, dtype=torch.int32)
@@ -45,7 +54,7 @@ class CacheStorage:
                                                 dtype=sdtype))
 
     def bytes(self) -> int:
-        return sum(t.numel() * t.element_size() for t in self.tensors)
+        return sum(t.numel() * t.element_size() for t in (*self.tensors, *self.value_tensors.values()))
 
     @property
     def max_tokens(self) -> int:
@@ -53,9 +62,12 @@ class CacheStorage:
         return min((t.shape[1] * self.manager.page_size for t in self.tables.values()), default=1 << 30)
 
     def pages(self, cache_slot: int) -> tuple[torch.Tensor, torch.Tensor]:
-        """(keys, values) of a cache slot, each ``[num_pages, kv_heads, page_size, head_dim]``."""
+        """(keys, values) of a cache slot, ``[num_pages, kv_heads, page_size, head_dim]`` (values: ``value_dim``)."""
         plan = self.manager.plan
-        t = self.tensors[plan.group_of_slot[cache_slot]][plan.index_in_group[cache_slot]]
+        g, i = plan.group_of_slot[cache_slot], plan.index_in_group[cache_slot]
+        if g in self.value_tensors:
+            return self.tensors[g][i], self.value_tensors[g][i]
+        t = self.tensors[g][i]
         return t[0], t[1]
 
     def state(self, cache_slot: int) -> torch.Tensor:

@@ -42,8 +42,10 @@ def _ensure_builtin() -> None:
 def family_of(cfg: Mapping[str, Any]) -> ModelFamily:
     _ensure_builtin()
     archs = cfg.get("architectures")
+    if archs is None and isinstance(cfg.get("architecture"), str):     # some designs name themselves with one string
+        archs = [cfg["architecture"]]
     if not isinstance(archs, (list, tuple)) or not archs or not isinstance(archs[0], str):
-        raise ConfigError("config key 'architectures' must be a non-empty list of names")
+        raise ConfigError("config key 'architectures' must be a non-empty list of names (or 'architecture' one name)")
     family = REGISTRY.get(archs[0])
     if family is None:
         raise ConfigError(

@@ -300,3 +300,100 @@ ACV_API int acv_add_bias(void* out, int ld, const float* bias, int rows, int N, 
         return ACV_ERR_DTYPE;
     return acv_launch_status();
 }
+
+// ----------------------------------------------------------------------------- a residual stream kept in float
+// Models whose residual sum is 32-bit in every run precision keep the stream x as float while the parts
+// read and write the run's element type T:  embedding rows times a constant into a float stream; the sum
+// x += delta and the norm in float, rounded once, at the norm's output; a constant times float logits.
+template <typename T>
+__global__ void embed_scaled_kernel(const T* __restrict__ table, const int* __restrict__ tokens, float* __restrict__ out,
+                                    int H, int V, float scale) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t = blockIdx.x;
+    int tok = tokens[t];
+    tok = tok < 0 ? 0 : (tok >= V ? V - 1 : tok);
+    const T* src = table + (size_t)tok * H;
+    float* dst = out + (size_t)t * H;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) dst[i] = to_f32(src[i]) * scale;
+}
+
+ACV_API int acv_embed_scaled(const void* table, const int* tokens, float* out, int T, int H, int V, float scale, int dtype,
+                             cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (dtype == ACV_F32)
+        acv_launch(PDL_MISC, embed_scaled_kernel<float>, T, 128, 0, stream, (const float*)table, tokens, out, H, V, scale);
+    else if (dtype == ACV_BF16)
+        acv_launch(PDL_MISC, embed_scaled_kernel<bf16>, T, 128, 0, stream, (const bf16*)table, tokens, out, H, V, scale);
+    else
+        return ACV_ERR_DTYPE;
+    return acv_launch_status();
+}
+
+// x float [*, H] (+= delta of type T, written back, unless rows are given); out (type T) = x * rsqrt(mean(x^2) + eps) * w,
+// all in float, one rounding.  The row waits in shared memory between the two passes.
+template <typename T>
+__global__ void add_rmsnorm_f32_kernel(float* __restrict__ x, const T* __restrict__ delta, const float* __restrict__ w,
+                                       T* __restrict__ out, const int* __restrict__ rows, int H, float eps) {
+    extern __shared__ float row[];
+    __shared__ float red[32];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int r_out = blockIdx.x;
+    const int r_in = rows ? rows[r_out] : r_out;
+    float* xr = x + (size_t)r_in * H;
+    const T* dr = delta ? delta + (size_t)r_in * H : nullptr;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        float v = xr[i];
+        if (dr) {
+            v += to_f32(dr[i]);
+            if (!rows) xr[i] = v;
+        }
+        row[i] = v;
+        ss += v * v;
+    }
+    ss = block_sum(ss, red);
+    const float rs = 1.f / sqrtf(ss / (float)H + eps);
+    T* o = out + (size_t)r_out * H;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = from_f32<T>(row[i] * rs * w[i]);
+}
+
+ACV_API int acv_add_rmsnorm_f32(float* x, const void* delta, const float* w, void* out, const int* rows, int n_rows, int H,
+                                float eps, int dtype, cudaStream_t stream) {
+    if (n_rows <= 0) return 0;
+    const size_t smem = (size_t)H * sizeof(float);
+    if (smem > 200 * 1024) return ACV_ERR_SIZE;
+    const int threads = H >= 4096 ? 512 : (H >= 1024 ? 256 : 128);
+    if (dtype == ACV_F32) {
+        if (smem > 48 * 1024) {
+            static AcvSmemConfig cfg;
+            const int e = acv_ensure_smem(cfg, add_rmsnorm_f32_kernel<float>, (int)smem);
+            if (e) return e;
+        }
+        acv_launch(PDL_NORM, add_rmsnorm_f32_kernel<float>, n_rows, threads, smem, stream, x, (const float*)delta, w, (float*)out, rows, H, eps);
+    } else if (dtype == ACV_BF16) {
+        if (smem > 48 * 1024) {
+            static AcvSmemConfig cfg;
+            const int e = acv_ensure_smem(cfg, add_rmsnorm_f32_kernel<bf16>, (int)smem);
+            if (e) return e;
+        }
+        acv_launch(PDL_NORM, add_rmsnorm_f32_kernel<bf16>, n_rows, threads, smem, stream, x, (const bf16*)delta, w, (bf16*)out, rows, H, eps);
+    } else {
+        return ACV_ERR_DTYPE;
+    }
+    return acv_launch_status();
+}
+
+__global__ void scale_f32_kernel(float* __restrict__ x, size_t n, float s) {
+    pdl_launch_dependents();
+    pdl_wait();
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) x[i] *= s;
+}
+
+ACV_API int acv_scale_f32(float* x, long long n, float s, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    const int blocks = (int)((n + 255) / 256 < 148 * 8 ? (n + 255) / 256 : 148 * 8);
+    acv_launch(PDL_MISC, scale_f32_kernel, blocks, 256, 0, stream, x, (size_t)n, s);
+    return acv_launch_status();
+}

@@ -1,0 +1,353 @@
+// Mixture of experts: routing, grouping of the tokens by expert, the experts' products, the sum.
+//
+//   z = W_r h (32-bit);  score = sigmoid(z) (or softmax(z));  the `top` largest scores choose the experts
+//   (ties go to the lower index); the chosen scores, as they are or divided by their sum, are the weights.
+//   An expert is a gated unit:  a = W_gate x, b = W_up x, y = act(a, b), out = W_down y.
+//   The weight w multiplies the expert's input (x = w h) or its output, as the model says.  With the
+//   weight on the input the products are linear in it, a = w (W_gate h), so the kernels multiply the
+//   accumulators by w, in 32-bit, instead of making scaled copies of h.
+//
+// The step is four launches whatever the routing turns out to be, so that it can be captured in a graph:
+//   acv_moe_route    one warp per token: router logits, scores, choice; also the shared expert's gate
+//   acv_moe_group    one block: rows (token, choice) counted per expert, each expert's rows padded to
+//                    whole tiles of MOE_TILE rows; a tile belongs to one expert
+//   acv_moe_gemm_*   tiles x column blocks: rows gathered by the grouping, the expert's weights by tile
+//   acv_moe_combine  per token: the chosen experts' outputs in the order of the choice, plus the
+//                    shared expert's output times its gate, summed in 32-bit
+#include "common.cuh"
+
+#define MOE_TILE 64          // rows of a tile of the grouped products (ops.MOE_TILE)
+
+// gated activation of an expert (ops.GLU_*)
+#define GLU_SWISH_CLAMPED 0  // g = min(a, limit), u = clamp(b, -limit, limit): g * sigmoid(alpha g) * (u + 1)
+
+template <typename T> __device__ __forceinline__ float sigmoid_f32(float x);
+template <> __device__ __forceinline__ float sigmoid_f32<float>(float x) { return 1.f / (1.f + expf(-x)); }
+template <> __device__ __forceinline__ float sigmoid_f32<bf16>(float x) { return __fdividef(1.f, 1.f + __expf(-x)); }
+
+template <typename T>
+__device__ __forceinline__ float glu_act(float a, float b, float limit, float alpha) {
+    const float g = fminf(a, limit);
+    const float u = fminf(fmaxf(b, -limit), limit);
+    return g * sigmoid_f32<T>(alpha * g) * (u + 1.f);
+}
+
+// ----------------------------------------------------------------------------- routing
+#define MR_WARPS 4
+// scores in shared memory, E floats per warp.  ids/weights: [T, top].  gate_w (optional, [H]): the shared
+// expert's gate, sigmoid(<gate_w, h>), one number per token.
+template <typename T>
+__global__ void moe_route_kernel(const T* __restrict__ h, int h_stride, const float* __restrict__ w_router,
+                                 const float* __restrict__ gate_w, int T_tokens, int H, int E, int top, int softmax,
+                                 int renorm, int* __restrict__ ids, float* __restrict__ weights, float* __restrict__ gate) {
+    extern __shared__ float sm_all[];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t = blockIdx.x * MR_WARPS + warp;
+    if (t >= T_tokens) return;
+    float* sc = sm_all + warp * E;
+    const T* row = h + (size_t)t * h_stride;
+    for (int e = 0; e < E; ++e) {
+        const float* wr = w_router + (size_t)e * H;
+        float d = 0.f;
+        for (int k = lane; k < H; k += 32) d = fmaf(to_f32(row[k]), wr[k], d);
+        d = warp_sum(d);
+        if (lane == 0) sc[e] = d;
+    }
+    if (gate_w) {
+        float d = 0.f;
+        for (int k = lane; k < H; k += 32) d = fmaf(to_f32(row[k]), gate_w[k], d);
+        d = warp_sum(d);
+        if (lane == 0) gate[t] = 1.f / (1.f + expf(-d));
+    }
+    __syncwarp();
+    if (softmax) {
+        float mx = -INFINITY;
+        for (int e = lane; e < E; e += 32) mx = fmaxf(mx, sc[e]);
+        mx = warp_max(mx);
+        float sum = 0.f;
+        for (int e = lane; e < E; e += 32) {
+            const float x = expf(sc[e] - mx);
+            sc[e] = x;
+            sum += x;
+        }
+        sum = warp_sum(sum);
+        __syncwarp();
+        for (int e = lane; e < E; e += 32) sc[e] /= sum;
+    } else {
+        for (int e = lane; e < E; e += 32) sc[e] = 1.f / (1.f + expf(-sc[e]));
+    }
+    __syncwarp();
+    float total = 0.f;
+    for (int j = 0; j < top; ++j) {
+        float best = -INFINITY;
+        int arg = 0x7fffffff;
+        for (int e = lane; e < E; e += 32) {
+            const float x = sc[e];
+            if (x > best) { best = x; arg = e; }       // ascending e: the first of equal scores stays
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oa = __shfl_xor_sync(0xffffffffu, arg, o);
+            if (ob > best || (ob == best && oa < arg)) { best = ob; arg = oa; }
+        }
+        if (arg == 0x7fffffff) arg = 0;     // top > E, or scores that are not numbers: never an index outside
+        if (lane == 0) {
+            ids[(size_t)t * top + j] = arg;
+            weights[(size_t)t * top + j] = best;
+            sc[arg] = -INFINITY;
+        }
+        total += best;
+        __syncwarp();
+    }
+    if (renorm && lane == 0)
+        for (int j = 0; j < top; ++j) weights[(size_t)t * top + j] /= total;
+}
+
+ACV_API int acv_moe_route(const void* h, int h_stride, const float* w_router, const float* gate_w, int T_tokens, int H, int E,
+                          int top, int softmax, int renorm, int* ids, float* weights, float* gate, int dtype,
+                          cudaStream_t stream) {
+    if (T_tokens <= 0) return 0;
+    if (E <= 0 || top <= 0 || top > E || E > 4096) return ACV_ERR_SIZE;
+    const size_t smem = (size_t)MR_WARPS * E * sizeof(float);
+    const int grid = (T_tokens + MR_WARPS - 1) / MR_WARPS;
+    if (dtype == ACV_F32)
+        acv_launch(PDL_MISC, moe_route_kernel<float>, grid, MR_WARPS * 32, smem, stream, (const float*)h, h_stride, w_router,
+                   gate_w, T_tokens, H, E, top, softmax, renorm, ids, weights, gate);
+    else if (dtype == ACV_BF16)
+        acv_launch(PDL_MISC, moe_route_kernel<bf16>, grid, MR_WARPS * 32, smem, stream, (const bf16*)h, h_stride, w_router,
+                   gate_w, T_tokens, H, E, top, softmax, renorm, ids, weights, gate);
+    else
+        return ACV_ERR_DTYPE;
+    return acv_launch_status();
+}
+
+// ----------------------------------------------------------------------------- grouping by expert
+// N = T * top rows (row r = token r / top, choice r % top).  Expert e's rows take the positions
+// [start[e], start[e] + count[e]) of the grouped list, start[e] a multiple of MOE_TILE; the positions up
+// to the next multiple hold -1.  tile_expert[i] names the expert of tile i (-1: no such tile).
+// The order of an expert's rows among themselves is whatever the atomics make it; a row's result does
+// not depend on its place.
+__global__ void moe_group_kernel(const int* __restrict__ ids, int N, int E, int max_tiles, int* __restrict__ grouped,
+                                 int* __restrict__ place, int* __restrict__ tile_expert) {
+    extern __shared__ int sm_int[];
+    int* count = sm_int;          // [E]
+    int* start = sm_int + E;      // [E + 1]
+    pdl_launch_dependents();
+    pdl_wait();
+    for (int e = threadIdx.x; e < E; e += blockDim.x) count[e] = 0;
+    for (int i = threadIdx.x; i < max_tiles * MOE_TILE; i += blockDim.x) grouped[i] = -1;
+    for (int i = threadIdx.x; i < max_tiles; i += blockDim.x) tile_expert[i] = -1;
+    __syncthreads();
+    for (int r = threadIdx.x; r < N; r += blockDim.x) {
+        const int e = ids[r];
+        if (e >= 0 && e < E) atomicAdd(&count[e], 1);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int at = 0;
+        for (int e = 0; e < E; ++e) {
+            start[e] = at;
+            at += (count[e] + MOE_TILE - 1) / MOE_TILE * MOE_TILE;
+        }
+        start[E] = at;
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < E; e += blockDim.x) {
+        for (int i = start[e] / MOE_TILE; i < start[e + 1] / MOE_TILE; ++i)
+            if (i < max_tiles) tile_expert[i] = e;
+        count[e] = 0;       // now the cursor inside the expert's rows
+    }
+    __syncthreads();
+    for (int r = threadIdx.x; r < N; r += blockDim.x) {
+        const int e = ids[r];
+        if (e < 0 || e >= E) { place[r] = -1; continue; }
+        const int at = start[e] + atomicAdd(&count[e], 1);
+        place[r] = at;
+        grouped[at] = r;
+    }
+}
+
+ACV_API int acv_moe_group(const int* ids, int N, int E, int max_tiles, int* grouped, int* place, int* tile_expert,
+                          cudaStream_t stream) {
+    if (N <= 0) return 0;
+    if (E <= 0 || E > 4096 || max_tiles < (N + MOE_TILE - 1) / MOE_TILE + E) return ACV_ERR_SIZE;
+    acv_launch(PDL_MISC, moe_group_kernel, 1, 1024, (size_t)(2 * E + 1) * sizeof(int), stream, ids, N, E, max_tiles, grouped, place,
+               tile_expert);
+    return acv_launch_status();
+}
+
+// ----------------------------------------------------------------------------- grouped products on the CUDA cores
+// Tile i (MOE_TILE rows of the grouped list) x 64 output columns; 256 threads, each a 4 x 4 micro-tile.
+// GLU: the expert's matrix is [2 * N, K], gate rows then up rows; row r of A is token grouped[r] / top; the
+//      accumulators are multiplied by the row's weight (when given) and go through the activation; output T.
+// else: A's row r is row r of the grouped list itself (the activations of the product before); output float,
+//      multiplied by the row's weight when given (the weight on the expert's output).
+// Sums run over k in ascending order inside fixed slabs of 16: a row's result does not depend on the others.
+template <typename T, bool GLU>
+__global__ void __launch_bounds__(256)
+moe_gemm_simt_kernel(const T* __restrict__ A, int lda, const T* __restrict__ W, long long w_expert_stride, int ldw,
+                     void* __restrict__ C, int ldc, const int* __restrict__ grouped, const int* __restrict__ tile_expert,
+                     const float* __restrict__ row_weight, int top, int N, int K, float limit, float alpha) {
+    __shared__ float As[16][MOE_TILE + 4];
+    __shared__ float Ws[16][64 + 4];
+    __shared__ float Us[GLU ? 16 : 1][64 + 4];
+    __shared__ int src[MOE_TILE];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int tile = blockIdx.y;
+    const int expert = tile_expert[tile];
+    if (expert < 0) return;
+    const int tid = threadIdx.x;
+    const int n0 = blockIdx.x * 64;
+    if (tid < MOE_TILE) src[tid] = grouped[tile * MOE_TILE + tid];
+    __syncthreads();
+    const T* We = W + (size_t)expert * w_expert_stride;
+    const int tx = tid & 15, ty = tid >> 4;
+    float acc[4][4], acu[GLU ? 4 : 1][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            acc[i][j] = 0.f;
+            if constexpr (GLU) acu[i][j] = 0.f;
+        }
+    for (int k0 = 0; k0 < K; k0 += 16) {
+#pragma unroll
+        for (int it = 0; it < 4; ++it) {
+            const int idx = tid + it * 256;
+            const int r = idx >> 4, kk = idx & 15;
+            const int gk = k0 + kk, gn = n0 + r;
+            const int s = src[r];
+            const long long arow = GLU ? (s >= 0 ? s / top : -1) : (s >= 0 ? tile * MOE_TILE + r : -1);
+            As[kk][r] = (arow >= 0 && gk < K) ? to_f32(A[(size_t)arow * lda + gk]) : 0.f;
+            Ws[kk][r] = (gn < N && gk < K) ? to_f32(We[(size_t)gn * ldw + gk]) : 0.f;
+            if constexpr (GLU) Us[kk][r] = (gn < N && gk < K) ? to_f32(We[(size_t)(N + gn) * ldw + gk]) : 0.f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < 16; ++kk) {
+            float a[4], b[4], u[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) a[i] = As[kk][ty * 4 + i];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                b[j] = Ws[kk][tx * 4 + j];
+                if constexpr (GLU) u[j] = Us[kk][tx * 4 + j];
+            }
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+                    if constexpr (GLU) acu[i][j] = fmaf(a[i], u[j], acu[i][j]);
+                }
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int r = ty * 4 + i;
+        const int s = src[r];
+        if (s < 0) continue;
+        const float w = row_weight ? row_weight[s] : 1.f;
+        const size_t crow = (size_t)(tile * MOE_TILE + r) * ldc;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int gn = n0 + tx * 4 + j;
+            if (gn >= N) continue;
+            if constexpr (GLU)
+                ((T*)C)[crow + gn] = from_f32<T>(glu_act<T>(acc[i][j] * w, acu[i][j] * w, limit, alpha));
+            else
+                ((float*)C)[crow + gn] = acc[i][j] * w;
+        }
+    }
+}
+
+// which: 0 = gate/up with activation (C of A's type), 1 = down (C float)
+ACV_API int acv_moe_gemm_simt(const void* A, int lda, const void* W, long long w_expert_stride, int ldw, void* C, int ldc,
+                              const int* grouped, const int* tile_expert, const float* row_weight, int top, int max_tiles,
+                              int N, int K, int which, float limit, float alpha, int dtype, cudaStream_t stream) {
+    if (max_tiles <= 0 || N <= 0) return 0;
+    if (K <= 0 || top <= 0 || max_tiles > 65535) return ACV_ERR_SIZE;
+    dim3 grid((N + 63) / 64, max_tiles);
+#define MG_LAUNCH(TT, G)                                                                                              \
+    acv_launch(PDL_GEMM, moe_gemm_simt_kernel<TT, G>, grid, 256, 0, stream, (const TT*)A, lda, (const TT*)W,          \
+               w_expert_stride, ldw, C, ldc, grouped, tile_expert, row_weight, top, N, K, limit, alpha)
+    if (dtype == ACV_F32) {
+        if (which == 0) MG_LAUNCH(float, true); else MG_LAUNCH(float, false);
+    } else if (dtype == ACV_BF16) {
+        if (which == 0) MG_LAUNCH(bf16, true); else MG_LAUNCH(bf16, false);
+    } else {
+        return ACV_ERR_DTYPE;
+    }
+#undef MG_LAUNCH
+    return acv_launch_status();
+}
+
+// ----------------------------------------------------------------------------- the sum
+// out[t] = sum over the token's choices, in their order, of D[place[t * top + j]]  (+ gate[t] * S[t]),
+// summed in 32-bit, rounded once to T.
+template <typename T>
+__global__ void moe_combine_kernel(const float* __restrict__ D, int ldd, const int* __restrict__ place, int top,
+                                   const T* __restrict__ S, int lds, const float* __restrict__ gate, T* __restrict__ out,
+                                   int ldo, int H) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t = blockIdx.x;
+    for (int c = threadIdx.x; c < H; c += blockDim.x) {
+        float sum = 0.f;
+        for (int j = 0; j < top; ++j) {
+            const int at = place[(size_t)t * top + j];
+            if (at >= 0) sum += D[(size_t)at * ldd + c];
+        }
+        if (S) sum += (gate ? gate[t] : 1.f) * to_f32(S[(size_t)t * lds + c]);
+        out[(size_t)t * ldo + c] = from_f32<T>(sum);
+    }
+}
+
+ACV_API int acv_moe_combine(const float* D, int ldd, const int* place, int top, const void* S, int lds, const float* gate,
+                            void* out, int ldo, int T_tokens, int H, int dtype, cudaStream_t stream) {
+    if (T_tokens <= 0 || H <= 0) return 0;
+    const int threads = H >= 1024 ? 256 : 128;
+    if (dtype == ACV_F32)
+        acv_launch(PDL_MISC, moe_combine_kernel<float>, T_tokens, threads, 0, stream, D, ldd, place, top, (const float*)S, lds,
+                   gate, (float*)out, ldo, H);
+    else if (dtype == ACV_BF16)
+        acv_launch(PDL_MISC, moe_combine_kernel<bf16>, T_tokens, threads, 0, stream, D, ldd, place, top, (const bf16*)S, lds, gate,
+                   (bf16*)out, ldo, H);
+    else
+        return ACV_ERR_DTYPE;
+    return acv_launch_status();
+}
+
+// ----------------------------------------------------------------------------- gated activation of a stacked product
+// gu [T, 2I]: gate columns, then up columns (one expert applied to every token, e.g. a shared expert).
+template <typename T>
+__global__ void glu_kernel(const T* __restrict__ gu, int ldg, T* __restrict__ out, int ldo, int I, size_t total, float limit,
+                           float alpha) {
+    pdl_launch_dependents();
+    pdl_wait();
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+        const size_t t = idx / I;
+        const int i = (int)(idx - t * I);
+        out[t * ldo + i] = from_f32<T>(glu_act<T>(to_f32(gu[t * ldg + i]), to_f32(gu[t * ldg + I + i]), limit, alpha));
+    }
+}
+
+ACV_API int acv_glu(const void* gu, int ldg, void* out, int ldo, int T_tokens, int I, int kind, float limit, float alpha,
+                    int dtype, cudaStream_t stream) {
+    const size_t total = (size_t)T_tokens * I;
+    if (total == 0) return 0;
+    if (kind != GLU_SWISH_CLAMPED) return ACV_ERR_SIZE;
+    const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+    if (dtype == ACV_F32)
+        acv_launch(PDL_ACT, glu_kernel<float>, blocks, 256, 0, stream, (const float*)gu, ldg, (float*)out, ldo, I, total, limit, alpha);
+    else if (dtype == ACV_BF16)
+        acv_launch(PDL_ACT, glu_kernel<bf16>, blocks, 256, 0, stream, (const bf16*)gu, ldg, (bf16*)out, ldo, I, total, limit, alpha);
+    else
+        return ACV_ERR_DTYPE;
+    return acv_launch_status();
+}

@@ -150,7 +150,7 @@ class Engine:
         per_page = state_bytes = 0
         for need in self.model.cache_plan().needs:
             if need is not None and need.kind == "paged":
-                per_page += 2 * need.num_kv_heads * need.head_dim * self.page_size * self.model.rt.dtype.itemsize
+                per_page += need.num_kv_heads * (need.head_dim + need.value_size) * self.page_size * self.model.rt.dtype.itemsize
             elif need is not None:       # state of fixed size: a slot for each request (and one for nobody)
                 n = 1
                 for d in need.shape:

@@ -78,6 +78,16 @@ def _declare(lib: ctypes.CDLL) -> None:
         "acv_attention_tc": [P, I, I, P, I, P, P, P, P, I, P, P, P, I, P, I, I, I, I, I, F, I, P, P],
         "acv_attention_chunk": [P, I, P, I, P, P, P, P, I, P, P, P, I, P, I, I, I, I, I, F, I, I, P],
         "acv_table_update": [P, I, I, P, I, P],
+        "acv_embed_scaled": [P, P, P, I, I, I, F, I, P],
+        "acv_add_rmsnorm_f32": [P, P, P, P, P, I, I, F, I, P],
+        "acv_scale_f32": [P, LL, F, P],
+        "acv_heads_norm_append": [P, P, P, I, I, I, I, I, I, I, P, P, F, P, P, P, I, P, P, P, I, I, I, P],
+        "acv_diff_attention_generic": [P, I, P, I, P, P, P, P, P, I, P, I, I, I, I, I, I, I, F, I, I, F, F, F, I, P],
+        "acv_moe_route": [P, I, P, P, I, I, I, I, I, I, P, P, P, I, P],
+        "acv_moe_group": [P, I, I, I, P, P, P, P],
+        "acv_moe_gemm_simt": [P, I, P, LL, I, P, I, P, P, P, I, I, I, I, I, F, F, I, P],
+        "acv_moe_combine": [P, I, P, I, P, I, P, P, I, I, I, I, P],
+        "acv_glu": [P, I, P, I, I, I, I, F, F, I, P],
         "acv_argmax": [P, I, I, I, P, P],
         "acv_apply_penalties": [P, I, I, P, P, P, I, P, P, P, P],
         "acv_sample": [P, I, I, I, P, P, P, P, P, P, P, P, P],
@@ -889,3 +899,168 @@ def linear_bf16_f32out(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, stat
     if gemm_tc_takes(x, w):
         return gemm_tc(x, w, out, static_weights=static_weights)
     return gemm_simt(x, w, out)
+
+
+# ----------------------------------------------------------------------------- a residual stream kept in float
+def embed_scaled(table: torch.Tensor, tokens: torch.Tensor, out: torch.Tensor, scale: float) -> torch.Tensor:
+    """out[t] = table[tokens[t]] * scale, out float32 [T, H] whatever the table's type."""
+    _need_cuda(table, tokens, out)
+    if out.dtype != torch.float32 or not out.is_contiguous() or not table.is_contiguous():
+        raise KernelError("embed_scaled: a contiguous float32 output and a contiguous table are wanted")
+    T, H = out.shape
+    _check(library().acv_embed_scaled(_p(table), _p(tokens), _p(out), T, H, table.shape[0], scale, dtype_code(table.dtype),
+                                      _stream()), "embed_scaled")
+    return out
+
+
+def add_rmsnorm_f32(x: torch.Tensor, delta: torch.Tensor | None, weight: torch.Tensor, eps: float, out: torch.Tensor,
+                    rows: torch.Tensor | None = None) -> torch.Tensor:
+    """The float32 stream x += delta (of out's type; in place, unless ``rows``); out = x / sqrt(mean(x^2) + eps) * weight,
+    computed in float32 and rounded once to out's type."""
+    _need_cuda(x, out, weight)
+    if x.dtype != torch.float32 or (delta is not None and delta.dtype != out.dtype) or not x.is_contiguous() \
+            or not out.is_contiguous() or (delta is not None and not delta.is_contiguous()):
+        raise KernelError("add_rmsnorm_f32: a contiguous float32 stream and a delta of the output's type are wanted")
+    n = out.shape[0] if rows is not None else x.shape[0]
+    _check(library().acv_add_rmsnorm_f32(_p(x), _p(delta), _p(weight), _p(out), _p(rows), n, x.shape[-1], eps,
+                                         dtype_code(out.dtype), _stream()), "add_rmsnorm_f32")
+    return out
+
+
+def scale_f32(x: torch.Tensor, s: float) -> torch.Tensor:
+    """x *= s in place (float32, contiguous)."""
+    _need_cuda(x)
+    if x.dtype != torch.float32 or not x.is_contiguous():
+        raise KernelError("scale_f32: a contiguous float32 tensor is wanted")
+    _check(library().acv_scale_f32(_p(x), x.numel(), s, _stream()), "scale_f32")
+    return x
+
+
+# ----------------------------------------------------------------------------- differential attention
+def heads_norm_append(qkv: torch.Tensor, num_q_vectors: int, num_k_vectors: int, num_kv_heads: int, dim: int, value_dim: int,
+                      q_weight: torch.Tensor | None, k_weight: torch.Tensor | None, eps: float, positions: torch.Tensor,
+                      seq_of_token: torch.Tensor, block_table: torch.Tensor | None, k_pages: torch.Tensor | None,
+                      v_pages: torch.Tensor | None, table_rows: torch.Tensor | None = None) -> None:
+    """RMS norm of each of the ``num_q_vectors`` query vectors of ``dim`` elements at the head of a row of ``qkv``
+    (in place) and, when pages are given, of the ``num_k_vectors`` key vectors behind them (written into the key
+    pages, ``num_k_vectors / num_kv_heads`` vectors to a key row) and the copy of the ``num_kv_heads`` value rows of
+    ``value_dim`` elements behind those into the value pages.  Without pages the row holds queries only."""
+    _need_cuda(qkv)
+    T = qkv.shape[0]
+    keeps = k_pages is not None
+    q_width = num_q_vectors * dim
+    k = qkv[:, q_width:] if keeps else None
+    v = qkv[:, q_width + num_k_vectors * dim:] if keeps else None
+    _check(library().acv_heads_norm_append(
+        _p(qkv), _p(k), _p(v), qkv.stride(0), T, num_q_vectors, num_k_vectors, num_kv_heads, dim, value_dim,
+        _p(q_weight), _p(k_weight), eps, _p(positions), _p(seq_of_token), _p(block_table),
+        block_table.stride(0) if block_table is not None else 0, _p(table_rows), _p(k_pages), _p(v_pages),
+        k_pages.shape[2] if keeps else 1, k_pages.shape[0] if keeps else 0, dtype_code(qkv.dtype), _stream()),
+        "heads_norm_append")
+
+
+def diff_attention_generic(q: torch.Tensor, out: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
+                           positions: torch.Tensor, seq_of_token: torch.Tensor, block_table: torch.Tensor, num_heads: int,
+                           num_kv_heads: int, dim: int, value_dim: int, scale: float, lam: float, eps: float,
+                           out_scale: float, window: int = 0, chunk: int = 0,
+                           table_rows: torch.Tensor | None = None) -> torch.Tensor:
+    """Differential attention of every token of the step: q rows hold ``num_heads`` pairs of query vectors, key pages
+    [pages, kv_heads, page, 2 * dim], value pages [pages, kv_heads, page, value_dim]; out rows ``num_heads * value_dim``."""
+    _need_cuda(q, out, k_pages, v_pages)
+    _check(library().acv_diff_attention_generic(
+        _p(q), q.stride(0), _p(out), out.stride(0), _p(k_pages), _p(v_pages), _p(positions), _p(seq_of_token),
+        _p(block_table), block_table.stride(0), _p(table_rows), q.shape[0], num_heads, num_kv_heads, dim, value_dim,
+        k_pages.shape[2], k_pages.shape[0], scale, window, chunk, lam, eps, out_scale, dtype_code(q.dtype), _stream()),
+        "diff_attention_generic")
+    return out
+
+
+def diff_attention(qkv: torch.Tensor, out: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, ctx,
+                   block_table: torch.Tensor, num_heads: int, num_kv_heads: int, dim: int, value_dim: int, scale: float,
+                   lam: float, eps: float, out_scale: float, window: int = 0, chunk: int = 0,
+                   work: dict | None = None) -> torch.Tensor:
+    """Differential attention of every token of the step over its request's pages (queries: the first
+    ``num_heads * 2 * dim`` columns of ``qkv``, after their norm); dispatch by shape."""
+    rows = getattr(ctx, "table_rows", None)
+    return diff_attention_generic(qkv, out, k_pages, v_pages, ctx.positions, ctx.seq_of_token, block_table, num_heads,
+                                  num_kv_heads, dim, value_dim, scale, lam, eps, out_scale, window, chunk, table_rows=rows)
+
+
+# ----------------------------------------------------------------------------- mixture of experts
+MOE_TILE = 64               # rows of a tile of the grouped products (MOE_TILE of csrc/moe.cu)
+GLU_SWISH_CLAMPED = 0       # g = min(a, limit), u = clamp(b, +-limit): g * sigmoid(alpha g) * (u + 1)
+
+
+def moe_max_tiles(rows: int, experts: int) -> int:
+    """Tiles that ``rows`` (token, choice) rows can need at most, whatever the routing: every expert may leave one
+    tile partly filled."""
+    return -(-rows // MOE_TILE) + experts
+
+
+def moe_route(h: torch.Tensor, w_router: torch.Tensor, gate_w: torch.Tensor | None, top: int, softmax: bool, renorm: bool,
+              ids: torch.Tensor, weights: torch.Tensor, gate: torch.Tensor | None) -> None:
+    """Router of a mixture of experts, in 32-bit: ids, weights [T, top] (int32, float32); gate [T] = sigmoid(h . gate_w)."""
+    _need_cuda(h, w_router, ids, weights)
+    if w_router.dtype != torch.float32 or not w_router.is_contiguous() or h.stride(1) != 1:
+        raise KernelError("moe_route: a contiguous float32 router matrix is wanted")
+    T, H = h.shape
+    _check(library().acv_moe_route(_p(h), h.stride(0), _p(w_router), _p(gate_w), T, H, w_router.shape[0], top, int(softmax),
+                                   int(renorm), _p(ids), _p(weights), _p(gate), dtype_code(h.dtype), _stream()), "moe_route")
+
+
+def moe_group(ids: torch.Tensor, experts: int, grouped: torch.Tensor, place: torch.Tensor, tile_expert: torch.Tensor) -> None:
+    """Group the rows (token, choice) by expert: ``grouped`` [tiles * MOE_TILE] holds the rows expert after expert, each
+    expert's padded with -1 to whole tiles; ``place`` [rows] where a row went; ``tile_expert`` [tiles] whose a tile is."""
+    _need_cuda(ids, grouped, place, tile_expert)
+    _check(library().acv_moe_group(_p(ids), ids.numel(), experts, tile_expert.numel(), _p(grouped), _p(place),
+                                   _p(tile_expert), _stream()), "moe_group")
+
+
+def moe_gemm_simt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, grouped: torch.Tensor, tile_expert: torch.Tensor,
+                  row_weight: torch.Tensor | None, top: int, glu: bool, limit: float = 0.0, alpha: float = 0.0) -> torch.Tensor:
+    """The experts' products over the grouped rows on the CUDA cores, 32-bit accumulation.
+
+    ``glu``: w [E, 2N, K] (gate rows, then up rows), a [T, K] the tokens, out [tiles * MOE_TILE, N] of a's type =
+    act(weight * gate, weight * up).  Otherwise w [E, N, K], a the grouped rows [tiles * MOE_TILE, K], out float32
+    [tiles * MOE_TILE, N] (times the row's weight, when given)."""
+    _need_cuda(a, w, out, grouped, tile_expert)
+    E, NW, K = w.shape
+    N = NW // 2 if glu else NW
+    if a.shape[1] != K or out.shape[1] != N or a.dtype != w.dtype or not w.is_contiguous() or a.stride(1) != 1 or \
+            out.stride(1) != 1 or out.dtype != (a.dtype if glu else torch.float32):
+        raise KernelError(f"moe_gemm_simt: shapes {tuple(a.shape)} x {tuple(w.shape)} -> {tuple(out.shape)} do not fit")
+    _check(library().acv_moe_gemm_simt(_p(a), a.stride(0), _p(w), w.stride(0), w.stride(1), _p(out), out.stride(0),
+                                       _p(grouped), _p(tile_expert), _p(row_weight), top, tile_expert.numel(), N, K,
+                                       0 if glu else 1, limit, alpha, dtype_code(a.dtype), _stream()), "moe_gemm_simt")
+    return out
+
+
+def moe_experts_up(h: torch.Tensor, gate_up: torch.Tensor, act: torch.Tensor, grouped: torch.Tensor, tile_expert: torch.Tensor,
+                   row_weight: torch.Tensor | None, top: int, limit: float, alpha: float) -> torch.Tensor:
+    """act[grouped row] = gated activation of the row's expert's gate and up products of its token; dispatch by shape."""
+    return moe_gemm_simt(h, gate_up, act, grouped, tile_expert, row_weight, top, True, limit, alpha)
+
+
+def moe_experts_down(act: torch.Tensor, down: torch.Tensor, out: torch.Tensor, grouped: torch.Tensor, tile_expert: torch.Tensor,
+                     row_weight: torch.Tensor | None, top: int) -> torch.Tensor:
+    """out[grouped row] (float32) = the row's expert's down product of its activations; dispatch by shape."""
+    return moe_gemm_simt(act, down, out, grouped, tile_expert, row_weight, top, False)
+
+
+def moe_combine(d: torch.Tensor, place: torch.Tensor, top: int, shared: torch.Tensor | None, gate: torch.Tensor | None,
+                out: torch.Tensor) -> torch.Tensor:
+    """out[t] = sum_j d[place[t, j]] (+ gate[t] * shared[t]), summed in float32 in the order of the choices."""
+    _need_cuda(d, place, out)
+    T, H = out.shape
+    _check(library().acv_moe_combine(_p(d), d.stride(0), _p(place), top, _p(shared), shared.stride(0) if shared is not None else 0,
+                                     _p(gate), _p(out), out.stride(0), T, H, dtype_code(out.dtype), _stream()), "moe_combine")
+    return out
+
+
+def glu(gate_up: torch.Tensor, out: torch.Tensor, kind: int, limit: float, alpha: float) -> torch.Tensor:
+    """out = act(gate_up[:, :I], gate_up[:, I:]) for a gated unit's stacked product [T, 2I]."""
+    _need_cuda(gate_up, out)
+    T, I = out.shape
+    _check(library().acv_glu(_p(gate_up), gate_up.stride(0), _p(out), out.stride(0), T, I, kind, limit, alpha,
+                             dtype_code(out.dtype), _stream()), "glu")
+    return out

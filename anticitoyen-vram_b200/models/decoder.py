@@ -92,7 +92,15 @@ class DecoderModel:
         for e in self.plan.schedule:
             if e.cache >= 0 and not e.writes:
                 need = self.blocks[e.layer].cache_need()
-                if needs[e.cache] is None or needs[e.cache] != need:
+                have = needs[e.cache]
+                if have is not None and have != need and hasattr(have, "widened") and hasattr(need, "widened"):
+                    # a reader that forgets by another rule than the writer (another window, another chunk size):
+                    # rows of the same sizes, and the slot keeps what either of them may read again
+                    try:
+                        needs[e.cache] = have = need = have.widened(need)
+                    except ValueError:
+                        pass
+                if have is None or have != need:
                     raise ValueError(f"layer {e.layer} reads cache slot {e.cache}, which no layer of equal need writes")
         return CachePlan(needs)
 
@@ -139,8 +147,15 @@ class DecoderModel:
         """Run the step's tokens through every scheduled layer; logits float32 [R, V] at ctx.logit_rows."""
         rt = self.rt
         plan = self.plan
-        x = torch.empty((ctx.num_tokens, plan.hidden_size), device=rt.device, dtype=rt.dtype)
-        ops.embed(self.embedding, ctx.tokens, x)
+        if plan.residual_dtype == "float32" or plan.embedding_scale != 1.0:
+            # the stream in float32 whatever the run's precision (a scaled embedding row is not rounded either)
+            if plan.residual_dtype != "float32" and rt.dtype != torch.float32:
+                raise ValueError("a scaled embedding is built for a float32 residual stream")
+            x = torch.empty((ctx.num_tokens, plan.hidden_size), device=rt.device, dtype=torch.float32)
+            ops.embed_scaled(self.embedding, ctx.tokens, x, plan.embedding_scale)
+        else:
+            x = torch.empty((ctx.num_tokens, plan.hidden_size), device=rt.device, dtype=rt.dtype)
+            ops.embed(self.embedding, ctx.tokens, x)
         delta = None
         cplan = storage.manager.plan
         for e in plan.schedule:
@@ -155,5 +170,9 @@ class DecoderModel:
             x, delta = self.blocks[e.layer].forward(x, delta, ctx, view)
         if ctx.num_logit_rows == 0:
             return torch.empty((0, plan.vocab_size), device=rt.device, dtype=torch.float32)
-        h = self.final_norm.forward(x, delta, rows=ctx.logit_rows)
-        return self.head(h, out_dtype=torch.float32)
+        kw = {"out_dtype": rt.dtype} if x.dtype != rt.dtype else {}
+        h = self.final_norm.forward(x, delta, rows=ctx.logit_rows, **kw)
+        logits = self.head(h, out_dtype=torch.float32)
+        if plan.logit_scale != 1.0:
+            ops.scale_f32(logits, plan.logit_scale)
+        return logits

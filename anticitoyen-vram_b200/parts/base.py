@@ -69,8 +69,10 @@ class Part:
 
 
 class Norm(Part):
-    def forward(self, x: torch.Tensor, delta: torch.Tensor | None, rows: torch.Tensor | None = None) -> torch.Tensor:
-        """x += delta in place (if given), return norm(x); with ``rows`` only those rows, x untouched."""
+    def forward(self, x: torch.Tensor, delta: torch.Tensor | None, rows: torch.Tensor | None = None,
+                out_dtype: torch.dtype | None = None) -> torch.Tensor:
+        """x += delta in place (if given), return norm(x); with ``rows`` only those rows, x untouched.
+        ``out_dtype``: the element type of the result where the stream x is kept in another (float32) one."""
         raise NotImplementedError
 
 

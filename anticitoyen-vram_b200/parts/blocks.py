@@ -23,9 +23,11 @@ class PreNormBlock:
         self.prefix = spec.prefix
         self.pre_mixer, self.pre_ff = spec.norm_prefixes
         self.input_norm = build("norm", spec.norm, hidden_size)
-        self.post_norm = build("norm", spec.norm, hidden_size)
         self.mixer = build("mixer", spec.mixer, hidden_size)
-        self.feed_forward = build("feed_forward", spec.feed_forward, hidden_size)
+        # a layer without a feed-forward is its mixer alone: x += mixer(norm(x))
+        self.post_norm = build("norm", spec.norm, hidden_size) if spec.feed_forward is not None else None
+        self.feed_forward = build("feed_forward", spec.feed_forward, hidden_size) if spec.feed_forward is not None else None
+        self.run_dtype = None
         # Small decode steps can run the whole layer as one persistent kernel (csrc/decode_layer.cu).  Off unless asked
         # for: measured on a B200 at the layer sizes of Qwen3-8B it is slower than the seven separate launches (a step's
         # time goes to the chain of dependent phases, which one kernel does not shorten).
@@ -35,33 +37,36 @@ class PreNormBlock:
         needs = {}
         for name, need in self.input_norm.tensor_needs().items():
             needs[self.pre_mixer + name] = need
-        for name, need in self.post_norm.tensor_needs().items():
-            needs[self.pre_ff + name] = need
         needs.update(self.mixer.tensor_needs())
-        needs.update(self.feed_forward.tensor_needs())
+        if self.feed_forward is not None:
+            for name, need in self.post_norm.tensor_needs().items():
+                needs[self.pre_ff + name] = need
+            needs.update(self.feed_forward.tensor_needs())
         return needs
 
     def load(self, tensors, rt: Runtime) -> None:
         sub = lambda p: {n[len(p):]: t for n, t in tensors.items() if n.startswith(p)}
+        self.run_dtype = rt.dtype
         self.input_norm.load(sub(self.pre_mixer), rt)
-        self.post_norm.load(sub(self.pre_ff), rt)
         self.mixer.load(tensors, rt)
-        self.feed_forward.load(tensors, rt)
+        if self.feed_forward is not None:
+            self.post_norm.load(sub(self.pre_ff), rt)
+            self.feed_forward.load(tensors, rt)
 
     def cache_need(self):
         return self.mixer.cache_need()
 
     def weight_bytes(self) -> int:
-        return sum(p.weight_bytes() for p in (self.input_norm, self.post_norm, self.mixer, self.feed_forward))
+        return sum(p.weight_bytes() for p in (self.input_norm, self.post_norm, self.mixer, self.feed_forward) if p is not None)
 
     def flops(self, num_tokens: int) -> float:
-        return self.mixer.flops(num_tokens) + self.feed_forward.flops(num_tokens)
+        return self.mixer.flops(num_tokens) + (self.feed_forward.flops(num_tokens) if self.feed_forward is not None else 0.0)
 
     def _fused_decode(self, x, delta, ctx, cache: CacheView | None):
         """A step of up to 16 one-token requests in bfloat16 runs the whole layer as one persistent kernel, when the
         parts are of the kinds that kernel knows (each part says so itself: ``decode_layer_spec``) and the sizes fit;
         None otherwise, and the parts run one by one."""
-        if x.dtype != torch.bfloat16 or cache is None or not cache.writes or ctx.max_q_len != 1:
+        if x.dtype != torch.bfloat16 or cache is None or not cache.writes or ctx.max_q_len != 1 or self.feed_forward is None:
             return None
         T = x.shape[0]
         if T > ops.DECODE_LAYER_TOKENS or T != ctx.num_seqs:
@@ -89,7 +94,11 @@ class PreNormBlock:
             fused = self._fused_decode(x, delta, ctx, cache)
             if fused is not None:
                 return fused
-        h = self.input_norm.forward(x, delta)
+        # a stream kept in float32 beside parts that run in bfloat16: the norms are told the parts' element type
+        kw = {"out_dtype": self.run_dtype} if self.run_dtype is not None and x.dtype != self.run_dtype else {}
+        h = self.input_norm.forward(x, delta, **kw)
         a = self.mixer.forward(h, ctx, cache)
-        h = self.post_norm.forward(x, a)
+        if self.feed_forward is None:
+            return x, a
+        h = self.post_norm.forward(x, a, **kw)
         return x, self.feed_forward.forward(h, ctx)

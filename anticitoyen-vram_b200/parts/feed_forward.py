@@ -69,3 +69,115 @@ class SwiGLU(FeedForward):
         act = torch.empty((h.shape[0], self.intermediate_size), device=h.device, dtype=h.dtype)
         ops.swiglu(gu, act)
         return self.down(act)
+
+
+@register("feed_forward", "moe")
+class RoutedExperts(FeedForward):
+    """Mixture of experts with an optional shared expert.
+
+    Router: z = W_r h in 32-bit; scores sigmoid(z) (``scoring`` "sigmoid") or softmax(z) ("softmax"); the ``top``
+    largest choose the experts (ties: the lower index); their scores are the weights, divided by their sum with
+    ``renormalize``.  An expert is a gated unit with clamps,
+
+        g = min(W_gate x, limit),  u = clamp(W_up x, -limit, limit),  y = g * sigmoid(alpha g) * (u + 1),  W_down y,
+
+    and the weight w multiplies its input (``weight_on`` "input": x = w h, which the kernels apply to the
+    accumulators of the first product, W (w h) = w (W h), in 32-bit) or its output ("output").  The shared expert
+    (``shared_ff`` > 0: the same unit with sizes and a limit of its own) runs for every token and is added times
+    sigmoid(<w_sg, h>), one number per token, computed in 32-bit with the router.
+
+    The step is the same launches whatever the routing is (rows grouped by expert on the device, tiles that belong
+    to no expert return at once), so it runs inside a captured graph.  Tensors behind ``prefix``: router, e<i>.gate,
+    e<i>.up, e<i>.down, shared.gate, shared.up, shared.down, shared.sg."""
+
+    def __init__(self, hidden_size: int, experts: int, top: int, expert_ff: int, expert_limit: float, shared_ff: int = 0,
+                 shared_limit: float = 0.0, alpha: float = 1.702, scoring: str = "sigmoid", renormalize: bool = False,
+                 weight_on: str = "input", prefix: str = "mlp.") -> None:
+        if scoring not in ("sigmoid", "softmax"):
+            raise ValueError(f"router scoring '{scoring}' is not built (sigmoid and softmax are)")
+        if weight_on not in ("input", "output"):
+            raise ValueError(f"weight_on must be 'input' or 'output', got '{weight_on}'")
+        if not 1 <= top <= experts:
+            raise ValueError(f"top {top} must lie in 1..{experts}")
+        self.hidden_size, self.experts, self.top = hidden_size, experts, top
+        self.expert_ff, self.expert_limit = expert_ff, float(expert_limit)
+        self.shared_ff, self.shared_limit = shared_ff, float(shared_limit)
+        self.alpha, self.scoring, self.renormalize, self.weight_on = float(alpha), scoring, bool(renormalize), weight_on
+        self.prefix = prefix
+
+    def tensor_needs(self):
+        H, F, p = self.hidden_size, self.expert_ff, self.prefix
+        needs = {p + "router": TensorNeed((self.experts, H))}
+        for e in range(self.experts):
+            needs[f"{p}e{e}.gate"] = TensorNeed((F, H))
+            needs[f"{p}e{e}.up"] = TensorNeed((F, H))
+            needs[f"{p}e{e}.down"] = TensorNeed((H, F))
+        if self.shared_ff:
+            S = self.shared_ff
+            needs.update({p + "shared.gate": TensorNeed((S, H)), p + "shared.up": TensorNeed((S, H)),
+                          p + "shared.down": TensorNeed((H, S)), p + "shared.sg": TensorNeed((1, H))})
+        return needs
+
+    def load(self, tensors, rt: Runtime) -> None:
+        p = self.prefix
+        w = lambda n: tensors[p + n].to(device=rt.device, dtype=rt.dtype)
+        self.router = tensors[p + "router"].to(device=rt.device, dtype=torch.float32).contiguous()
+        # [E, 2F, H]: an expert's gate rows, then its up rows; [E, H, F]
+        self.gate_up = torch.stack([torch.cat([w(f"e{e}.gate"), w(f"e{e}.up")], dim=0) for e in range(self.experts)]).contiguous()
+        self.down = torch.stack([w(f"e{e}.down") for e in range(self.experts)]).contiguous()
+        self.shared_gate_up = self.shared_down = self.shared_gate = None
+        if self.shared_ff:
+            self.shared_gate_up = Linear.stacked([w("shared.gate"), w("shared.up")])
+            self.shared_down = Linear(w("shared.down"))
+            self.shared_gate = tensors[p + "shared.sg"].to(device=rt.device, dtype=torch.float32).reshape(-1).contiguous()
+
+    # ---- cost of a step
+    def weight_bytes(self) -> int:
+        """All experts' weights: what a step reads once its tokens' choices cover them (a lower bound for few tokens
+        is ``active_weight_bytes``)."""
+        n = self.router.numel() * 4 + (self.gate_up.numel() + self.down.numel()) * self.gate_up.element_size()
+        if self.shared_ff:
+            n += self.shared_gate_up.weight_bytes() + self.shared_down.weight_bytes() + self.shared_gate.numel() * 4
+        return n
+
+    def active_weight_bytes(self, num_tokens: int) -> int:
+        """Weights that a step of ``num_tokens`` tokens reads at most: no more experts than rows."""
+        active = min(self.experts, num_tokens * self.top)
+        per = (self.gate_up.numel() + self.down.numel()) // self.experts * self.gate_up.element_size()
+        n = self.router.numel() * 4 + active * per
+        if self.shared_ff:
+            n += self.shared_gate_up.weight_bytes() + self.shared_down.weight_bytes() + self.shared_gate.numel() * 4
+        return n
+
+    def flops(self, num_tokens: int) -> float:
+        H = self.hidden_size
+        n = 2.0 * num_tokens * self.experts * H + 6.0 * num_tokens * self.top * self.expert_ff * H
+        return n + (6.0 * num_tokens * self.shared_ff * H if self.shared_ff else 0.0)
+
+    def forward(self, h, ctx):
+        T, H = h.shape
+        E, top, F = self.experts, self.top, self.expert_ff
+        dev = h.device
+        rows = T * top
+        tiles = ops.moe_max_tiles(rows, E)
+        ids = torch.empty(rows, device=dev, dtype=torch.int32)
+        weights = torch.empty(rows, device=dev, dtype=torch.float32)
+        gate = torch.empty(T, device=dev, dtype=torch.float32) if self.shared_ff else None
+        ops.moe_route(h, self.router, self.shared_gate, top, self.scoring == "softmax", self.renormalize, ids, weights, gate)
+        grouped = torch.empty(tiles * ops.MOE_TILE, device=dev, dtype=torch.int32)
+        place = torch.empty(rows, device=dev, dtype=torch.int32)
+        tile_expert = torch.empty(tiles, device=dev, dtype=torch.int32)
+        ops.moe_group(ids, E, grouped, place, tile_expert)
+        act = torch.empty((tiles * ops.MOE_TILE, F), device=dev, dtype=h.dtype)
+        ops.moe_experts_up(h, self.gate_up, act, grouped, tile_expert, weights if self.weight_on == "input" else None, top,
+                           self.expert_limit, self.alpha)
+        parts = torch.empty((tiles * ops.MOE_TILE, H), device=dev, dtype=torch.float32)
+        ops.moe_experts_down(act, self.down, parts, grouped, tile_expert, weights if self.weight_on == "output" else None, top)
+        shared = None
+        if self.shared_ff:
+            gu = self.shared_gate_up(h)
+            sact = torch.empty((T, self.shared_ff), device=dev, dtype=h.dtype)
+            ops.glu(gu, sact, ops.GLU_SWISH_CLAMPED, self.shared_limit, self.alpha)
+            shared = self.shared_down(sact)
+        out = torch.empty((T, H), device=dev, dtype=h.dtype)
+        return ops.moe_combine(parts, place, top, shared, gate, out)

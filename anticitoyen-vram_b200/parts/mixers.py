@@ -143,3 +143,129 @@ class Attention(Mixer):
         ops.attention(qkv, out, cache.k_pages, cache.v_pages, ctx, table, NH, NKV, D, self.scale, self.window,
                       work=ctx.work[self.metadata_key])
         return self.o(out)
+
+
+@register("mixer", "diff_attention")
+class DiffAttention(Mixer):
+    """Differential attention over the paged cache: every head has two query vectors and, per kv-head, two key
+    vectors of ``dim`` elements, [map 1 | map 2], and one value vector of ``value_dim``.  Each map is a softmax
+    attention of its own over the same values; a head's output is
+
+        o = o1 - lambda * o2,    lambda = exp(<lq1, lk1>) - exp(<lq2, lk2>) + diff      (one number for the layer)
+        out = o / sqrt(mean(o^2) + eps) * (1 - diff)                                     (over the head, no weight)
+
+    Query and key vectors are brought to unit RMS and multiplied by a weight of ``dim`` elements that all heads and
+    both maps share (``norm_eps`` None: no norm).  No position encoding: order enters through the mask alone, which
+    is causal, limited to the last ``window`` keys (``window`` > 0) and/or to the query's own chunk of ``chunk``
+    positions counted from the request's position 0 (``chunk`` > 0).  With ``own_kv`` false the layer has no key and
+    value projections and reads the cache slot that another layer writes (the plan's schedule says which).
+
+    Scores, both softmaxes, lambda and the head norm are 32-bit in every run precision.  ``names``: the tensors'
+    names behind ``prefix`` (default: q, k, v, o, q.norm, k.norm, lq1, lk1, lq2, lk2)."""
+
+    NAMES = {n: n for n in ("q", "k", "v", "o", "q.norm", "k.norm", "lq1", "lk1", "lq2", "lk2")}
+    metadata_key = "attention"      # the work lists of the attention kernels serve these layers as well
+
+    def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, dim: int, value_dim: int, scale: float | None,
+                 diff: float, norm_eps: float | None, chunk: int = 0, window: int = 0, own_kv: bool = True,
+                 prefix: str = "mix.", names: dict | None = None) -> None:
+        if num_heads % num_kv_heads:
+            raise ValueError(f"{num_heads} heads are not a multiple of {num_kv_heads} kv heads")
+        self.hidden_size = hidden_size
+        self.num_heads, self.num_kv_heads, self.dim, self.value_dim = num_heads, num_kv_heads, dim, value_dim
+        self.scale = float(scale) if scale is not None else dim ** -0.5
+        self.diff = float(diff)
+        self.norm_eps = norm_eps
+        self.chunk, self.window = int(chunk), int(window)
+        self.own_kv = own_kv
+        self.prefix = prefix
+        self.names = {**self.NAMES, **(names or {})}
+        self.q_size = num_heads * 2 * dim
+        self.k_size = num_kv_heads * 2 * dim
+        self.v_size = num_kv_heads * value_dim
+        self.lam = self.diff
+
+    def _n(self, role: str) -> str:
+        return self.prefix + self.names[role]
+
+    def cache_need(self):
+        return PagedNeed(self.num_kv_heads, 2 * self.dim, self.window,
+                         self.value_dim if self.value_dim != 2 * self.dim else 0, self.chunk)
+
+    def step_metadata(self, q_lens, kv_lens, cu_q) -> StepMetadata:
+        return StepMetadata(*ops.attention_work(q_lens, kv_lens, cu_q))
+
+    def decode_metadata(self, padded: int, max_kv: int) -> StepMetadata:
+        return StepMetadata(*ops.attention_work_decode(padded, max_kv))
+
+    def tensor_needs(self):
+        H = self.hidden_size
+        needs = {self._n("q"): TensorNeed((self.q_size, H)), self._n("o"): TensorNeed((H, self.num_heads * self.value_dim))}
+        if self.own_kv:
+            needs[self._n("k")] = TensorNeed((self.k_size, H))
+            needs[self._n("v")] = TensorNeed((self.v_size, H))
+        if self.norm_eps is not None:
+            needs[self._n("q.norm")] = TensorNeed((self.dim,), "norm")
+            if self.own_kv:
+                needs[self._n("k.norm")] = TensorNeed((self.dim,), "norm")
+        for role in ("lq1", "lk1", "lq2", "lk2"):
+            needs[self._n(role)] = TensorNeed((self.dim,))
+        return needs
+
+    def load(self, tensors, rt: Runtime) -> None:
+        w = lambda role: tensors[self._n(role)].to(device=rt.device, dtype=rt.dtype)
+        f = lambda role: tensors[self._n(role)].to(device=rt.device, dtype=torch.float32).contiguous()
+        self.qkv = Linear.stacked([w("q"), w("k"), w("v")]) if self.own_kv else Linear(w("q"))
+        self.o = Linear(w("o"))
+        self.q_norm = f("q.norm") if self.norm_eps is not None else None
+        self.k_norm = f("k.norm") if self.norm_eps is not None and self.own_kv else None
+        # lambda is a constant of the layer's weights: folded once, in 32-bit, when they are loaded
+        v = {role: tensors[self._n(role)].to(torch.float32) for role in ("lq1", "lk1", "lq2", "lk2")}
+        self.lam = (float(torch.exp((v["lq1"] * v["lk1"]).sum())) - float(torch.exp((v["lq2"] * v["lk2"]).sum()))
+                    + self.diff)
+
+    # ---- cost of a step
+    def weight_bytes(self) -> int:
+        norms = sum(t.numel() * 4 for t in (self.q_norm, self.k_norm) if t is not None)
+        return self.qkv.weight_bytes() + self.o.weight_bytes() + norms
+
+    def flops(self, num_tokens: int) -> float:
+        return self.qkv.flops(num_tokens) + self.o.flops(num_tokens)
+
+    def _seen(self, q: int, kv: int) -> float:
+        """Keys that the q queries at the end of a context of kv tokens see, summed over the queries."""
+        total = 0
+        for p in range(kv - q, kv):
+            lo = p // self.chunk * self.chunk if self.chunk > 0 else 0
+            if self.window > 0:
+                lo = max(lo, p - self.window + 1)
+            total += p - lo + 1
+        return float(total)
+
+    def mixing_flops(self, q_lens, kv_lens) -> float:
+        # two score products of dim and two weighted sums of value_dim for every (query, key) pair of a head
+        return 4.0 * self.num_heads * (self.dim + self.value_dim) * sum(self._seen(q, kv) for q, kv in zip(q_lens, kv_lens))
+
+    def cache_bytes_read(self, q_lens, kv_lens, itemsize: int) -> int:
+        keys = 0
+        for q, kv in zip(q_lens, kv_lens):
+            need = PagedNeed(1, 1, self.window, 0, self.chunk)
+            keys += kv - need.first_needed(kv - q)
+        return keys * (self.k_size + self.v_size) * itemsize
+
+    def forward(self, h, ctx, cache: CacheView):
+        NH, NKV, D, DV = self.num_heads, self.num_kv_heads, self.dim, self.value_dim
+        if cache.writes != self.own_kv:
+            raise ValueError("a diff_attention layer writes its cache slot exactly when it has key and value projections")
+        table = ctx.block_tables[cache.group]
+        rows = ctx.table_rows
+        qkv = self.qkv(h)
+        eps = self.norm_eps if self.norm_eps is not None else 0.0
+        if self.norm_eps is not None or self.own_kv:
+            ops.heads_norm_append(qkv, 2 * NH, 2 * NKV, NKV, D, DV, self.q_norm, self.k_norm, eps, ctx.positions,
+                                  ctx.seq_of_token, table if self.own_kv else None, cache.k_pages if self.own_kv else None,
+                                  cache.v_pages if self.own_kv else None, table_rows=rows)
+        out = torch.empty((qkv.shape[0], NH * DV), device=h.device, dtype=h.dtype)
+        ops.diff_attention(qkv, out, cache.k_pages, cache.v_pages, ctx, table, NH, NKV, D, DV, self.scale, self.lam, eps,
+                           1.0 - self.diff, self.window, self.chunk, work=ctx.work.get(self.metadata_key))
+        return self.o(out)

@@ -30,7 +30,7 @@ class LayerSpec:
     prefix: str          # tensor-name prefix of the layer, e.g. "model.layers.3."
     block: str           # arrangement of the parts, e.g. "prenorm"
     mixer: PartSpec
-    feed_forward: PartSpec
+    feed_forward: PartSpec | None   # None: the layer is its mixer alone (no second norm either)
     norm: PartSpec       # the norm placed before the mixer and before the feed-forward
     norm_prefixes: tuple[str, str] = ("input_layernorm.", "post_attention_layernorm.")
 
@@ -59,6 +59,11 @@ class ModelPlan:
     head_name: str = "lm_head.weight"
     tied_head: bool = False
     eos_token_ids: tuple[int, ...] = ()
+    embedding_scale: float = 1.0      # the embedding row is multiplied by this as it enters the stream
+    logit_scale: float = 1.0          # and the head's output by this
+    # "float32": the residual stream is float32 in every run precision (the sums x + delta are then never rounded to
+    # bfloat16); None: the stream has the run's element type
+    residual_dtype: str | None = None
 
     @property
     def num_cache_slots(self) -> int:
