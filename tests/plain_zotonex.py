@@ -73,25 +73,32 @@ def diff_lambda(w: dict, diff: float) -> float:
     return math.exp(float((w["lq1"] * w["lk1"]).sum())) - math.exp(float((w["lq2"] * w["lk2"]).sum())) + diff
 
 
-def diff_attention(h: torch.Tensor, w: dict, m: dict, eps: float, k: torch.Tensor, v: torch.Tensor) -> torch.Tensor:
-    """The mixer for one whole sequence, given the keys and values it reads (its own or another layer's)."""
-    T = h.shape[0]
-    H, G, dim, vdim = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
-    q = (h @ w["q"].T).view(T, H, 2, dim)
-    q = unit_rms(q, eps) * w["q.norm"]
-    seen = chunk_mask(T, (m.get("mask") or {}).get("size"))
-    lam = diff_lambda(w, m["diff"])
+def diff_core(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, seen: torch.Tensor, scale: float, lam: float,
+              diff: float, eps: float) -> torch.Tensor:
+    """q [T, H, 2, dim] and k [S, G, 2, dim] after their norms, v [S, G, vdim], seen [T, S] bool -> [T, H * vdim].
+    Each of a head's two maps is a softmax attention of its own over the same values; o = o1 - lam o2, brought to
+    unit RMS over the head and multiplied by 1 - diff."""
+    H, G = q.shape[1], k.shape[1]
     heads = []
     for hq in range(H):
         g = hq // (H // G)
         maps = []
         for a in range(2):
-            s = (q[:, hq, a] @ k[:, g, a].T) * m["scale"]
+            s = (q[:, hq, a] @ k[:, g, a].T) * scale
             s = s.masked_fill(~seen, float("-inf"))
             maps.append(torch.softmax(s, dim=-1) @ v[:, g])
-        o = maps[0] - lam * maps[1]
-        heads.append(unit_rms(o, eps) * (1.0 - m["diff"]))
-    return torch.cat(heads, dim=-1) @ w["o"].T
+        heads.append(unit_rms(maps[0] - lam * maps[1], eps) * (1.0 - diff))
+    return torch.cat(heads, dim=-1)
+
+
+def diff_attention(h: torch.Tensor, w: dict, m: dict, eps: float, k: torch.Tensor, v: torch.Tensor) -> torch.Tensor:
+    """The mixer for one whole sequence, given the keys and values it reads (its own or another layer's)."""
+    T = h.shape[0]
+    q = (h @ w["q"].T).view(T, m["heads"], 2, m["dim"])
+    q = unit_rms(q, eps) * w["q.norm"]
+    seen = chunk_mask(T, (m.get("mask") or {}).get("size"))
+    o = diff_core(q, k, v, seen, m["scale"], diff_lambda(w, m["diff"]), m["diff"], eps)
+    return o @ w["o"].T
 
 
 def expert(x: torch.Tensor, gate: torch.Tensor, up: torch.Tensor, down: torch.Tensor, limit: float) -> torch.Tensor:
@@ -149,3 +156,11 @@ def forward(cfg: dict, tensors: dict, ids, return_layers: bool = False):
     logits = (rms_norm(x, tensors["final.norm"], eps) @ tensors["head"].T) * cfg["logit_scale"]
     assert logits.dtype == dtype
     return (logits, torch.stack(after)) if return_layers else logits
+
+
+def greedy(cfg: dict, tensors: dict, prompt, new_tokens: int) -> list[int]:
+    """Greedy continuation, the whole sequence run again for every token."""
+    ids = list(prompt)
+    for _ in range(new_tokens):
+        ids.append(int(forward(cfg, tensors, ids)[-1].argmax()))
+    return ids[len(prompt):]
