@@ -25,7 +25,7 @@ attn_chunk_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ o
                   const bf16* __restrict__ k_pages, const bf16* __restrict__ v_pages, const int* __restrict__ tile_seq,
                   const int* __restrict__ tile_q0, const int* __restrict__ cu_q, const int* __restrict__ kv_len,
                   const int* __restrict__ block_table, int bt_stride, const int* __restrict__ bt_rows, int NH, int NKV, int page_size, int page_shift,
-                  int pg_cap, int num_pages, float scale, int window) {
+                  int pg_cap, int num_pages, float scale, int window, int chunk) {
     constexpr int CH = D / 8;
     constexpr int TILE_BYTES = AC_BN * D * 2;
     extern __shared__ __align__(128) unsigned char smem[];
@@ -46,7 +46,14 @@ attn_chunk_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ o
     const int pos0 = kv_len[seq] - q_len + q0;          // absolute position of the tile's first query
     const int* bt = block_table + (size_t)(bt_rows ? bt_rows[seq] : seq) * bt_stride;
     const int hi = pos0 + rows - 1;                     // last key any row of the tile sees
-    const int lo = window > 0 ? max(0, pos0 - window + 1) : 0;
+    // first key that a row at position x sees: the window's lower edge and/or the start of x's chunk (counted from the
+    // request's position 0); it grows with x
+    auto first_seen = [&](int x) {
+        int f = window > 0 ? max(0, x - window + 1) : 0;
+        if (chunk > 0) f = max(f, x / chunk * chunk);
+        return f;
+    };
+    const int lo = first_seen(pos0);
     const int j_first = lo & ~(AC_BN - 1);
     const int n_tiles = (hi - j_first) / AC_BN + 1;
 
@@ -128,6 +135,8 @@ attn_chunk_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ o
     const float scale_log2 = scale * AC_LOG2E;
     // absolute positions of this thread's two rows
     const int p_row[2] = {pos0 + warp * 16 + (lane >> 2), pos0 + warp * 16 + (lane >> 2) + 8};
+    const int lo_row[2] = {first_seen(p_row[0]), first_seen(p_row[1])};
+    const int lo_warp_first = first_seen(pos0 + warp * 16), lo_warp_last = first_seen(pos0 + warp * 16 + 15);
 
     for (int t = 0; t < n_tiles; ++t) {
         const int stage = t & 1;
@@ -139,7 +148,7 @@ attn_chunk_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ o
         const int j0 = j_first + t * AC_BN;
         // a warp whose rows all come before this tile's first key has nothing to do in it
         const bool active = j0 <= pos0 + warp * 16 + 15 && warp * 16 < rows &&
-                            (window <= 0 || j0 + AC_BN - 1 > pos0 + warp * 16 - window);
+                            j0 + AC_BN - 1 >= lo_warp_first;
         if (active) {
             float s[AC_BN / 8][4];
 #pragma unroll
@@ -158,8 +167,7 @@ attn_chunk_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ o
             }
             // Only tiles that cross a row's causal edge (or the window's lower edge) need the mask; the
             // scores stay unscaled: scale*log2(e) goes into the exponent's fused multiply-add.
-            const bool need_mask = !(j0 + AC_BN - 1 <= pos0 + warp * 16 &&
-                                     (window <= 0 || j0 > pos0 + warp * 16 + 15 - window));
+            const bool need_mask = !(j0 + AC_BN - 1 <= pos0 + warp * 16 && j0 >= lo_warp_last);
             float mx[2] = {-INFINITY, -INFINITY};
             if (need_mask) {
 #pragma unroll
@@ -168,7 +176,7 @@ attn_chunk_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ o
                     for (int e = 0; e < 4; ++e) {
                         const int j = j0 + nt * 8 + (lane & 3) * 2 + (e & 1);
                         const int p = p_row[e >> 1];
-                        const bool seen = j <= p && (window <= 0 || j > p - window);
+                        const bool seen = j <= p && j >= lo_row[e >> 1];
                         if (!seen) s[nt][e] = -INFINITY;
                     }
             }
@@ -246,7 +254,7 @@ template <int D>
 static int launch_chunk(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,
                         const void* v_pages, const int* tile_seq, const int* tile_q0, int n_tiles, const int* cu_q,
                         const int* kv_len, const int* block_table, int bt_stride, const int* bt_rows, int NH, int NKV, int page_size,
-                        int num_pages, float scale, int window, int max_kv, cudaStream_t stream) {
+                        int num_pages, float scale, int window, int chunk, int max_kv, cudaStream_t stream) {
     int page_shift = -1;
     for (int b = 0; b < 31; ++b)
         if ((1 << b) == page_size) page_shift = b;
@@ -258,7 +266,7 @@ static int launch_chunk(const void* q, int q_stride, void* out, int out_stride, 
     dim3 grid(n_tiles, NH);
     acv_launch(PDL_MISC, attn_chunk_kernel<D>, grid, AC_THREADS, smem, stream,
         (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)k_pages, (const bf16*)v_pages, tile_seq,
-        tile_q0, cu_q, kv_len, block_table, bt_stride, bt_rows, NH, NKV, page_size, page_shift, pg_cap, num_pages, scale, window);
+        tile_q0, cu_q, kv_len, block_table, bt_stride, bt_rows, NH, NKV, page_size, page_shift, pg_cap, num_pages, scale, window, chunk);
     return acv_launch_status();
 }
 
@@ -267,7 +275,7 @@ static int launch_chunk(const void* q, int q_stride, void* out, int out_stride, 
 ACV_API int acv_attention_chunk(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,
                                 const void* v_pages, const int* tile_seq, const int* tile_q0, int n_tiles,
                                 const int* cu_q, const int* kv_len, const int* block_table, int bt_stride, const int* bt_rows, int NH,
-                                int NKV, int D, int page_size, int num_pages, float scale, int window, int max_kv,
+                                int NKV, int D, int page_size, int num_pages, float scale, int window, int chunk, int max_kv,
                                 cudaStream_t stream) {
     if (n_tiles <= 0) return 0;
     if (NKV <= 0 || NH % NKV || NH > 65535) return ACV_ERR_SIZE;
@@ -275,7 +283,7 @@ ACV_API int acv_attention_chunk(const void* q, int q_stride, void* out, int out_
         ((uintptr_t)out & 3) || (out_stride & 1))
         return ACV_ERR_ALIGN;
 #define AC_ARGS q, q_stride, out, out_stride, k_pages, v_pages, tile_seq, tile_q0, n_tiles, cu_q, kv_len, block_table, \
-                bt_stride, bt_rows, NH, NKV, page_size, num_pages, scale, window, max_kv, stream
+                bt_stride, bt_rows, NH, NKV, page_size, num_pages, scale, window, chunk, max_kv, stream
     switch (D) {
         case 64: return launch_chunk<64>(AC_ARGS);
         case 128: return launch_chunk<128>(AC_ARGS);

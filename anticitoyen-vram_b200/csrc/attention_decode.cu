@@ -32,7 +32,7 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ 
                    const bf16* __restrict__ k_pages, const bf16* __restrict__ v_pages,
                    const int* __restrict__ dec_tokens, const int* __restrict__ dec_seqs,
                    const int* __restrict__ kv_len, const int* __restrict__ block_table, int bt_stride,
-                   const int* __restrict__ bt_rows, int NH, int NKV, int page_size, int page_shift, int pg_cap, int num_pages, float scale, int window, int n_splits,
+                   const int* __restrict__ bt_rows, int NH, int NKV, int page_size, int page_shift, int pg_cap, int num_pages, float scale, int window, int chunk_mask, int n_splits,
                    float* __restrict__ part_acc, float* __restrict__ part_ml, int* __restrict__ counters,
                    int cluster_merge) {
     constexpr int CH = D / 8;                 // 16-byte chunks per row
@@ -59,7 +59,9 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ 
     const int n_rep = NH / NKV;
     const int* bt = block_table + (size_t)(bt_rows ? bt_rows[seq] : seq) * bt_stride;   // the request's row of the table
     const int p = kv_len[seq] - 1;
-    const int lo = window > 0 ? max(0, p - window + 1) : 0;
+    // the first key the query sees: the window's lower edge and/or the start of its chunk (counted from position 0)
+    int lo = window > 0 ? max(0, p - window + 1) : 0;
+    if (chunk_mask > 0) lo = max(lo, p / chunk_mask * chunk_mask);
     const int n_keys = p + 1 - lo;
     const int chunk = (((n_keys + n_splits - 1) / n_splits) + AD_TILE - 1) & ~(AD_TILE - 1);
     const int beg = lo + split * chunk;
@@ -502,7 +504,7 @@ template <int D, int NW>
 static int launch_decode_with(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,
                               const void* v_pages, const int* dec_tokens, const int* dec_seqs, int n_dec, const int* kv_len,
                               const int* block_table, int bt_stride, const int* bt_rows, int NH, int NKV, int page_size,
-                              int page_shift, int pg_cap, int num_pages, float scale, int window, int n_splits,
+                              int page_shift, int pg_cap, int num_pages, float scale, int window, int chunk_mask, int n_splits,
                               float* part_acc, float* part_ml, int* counters, int cluster_merge, int smem,
                               cudaStream_t stream) {
     if (int rc = acv_ensure_smem(decode_smem_config<D, NW>(), attn_decode_kernel<D, NW>, smem)) return rc;
@@ -510,7 +512,7 @@ static int launch_decode_with(const void* q, int q_stride, void* out, int out_st
     acv_launch_cluster(PDL_ATTN, dim3(1, 1, cluster_merge ? n_splits : 1), attn_decode_kernel<D, NW>, grid, NW * 32, smem,
         stream, (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)k_pages, (const bf16*)v_pages, dec_tokens,
         dec_seqs, kv_len, block_table, bt_stride, bt_rows, NH, NKV, page_size, page_shift, pg_cap, num_pages, scale, window,
-        n_splits, part_acc, part_ml, counters, cluster_merge);
+        chunk_mask, n_splits, part_acc, part_ml, counters, cluster_merge);
     return acv_launch_status();
 }
 
@@ -518,7 +520,7 @@ template <int D>
 static int launch_decode(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,
                          const void* v_pages, const int* dec_tokens, const int* dec_seqs, int n_dec, const int* kv_len,
                          const int* block_table, int bt_stride, const int* bt_rows, int NH, int NKV, int page_size,
-                         int num_pages, float scale, int window, int n_splits, float* part_acc, float* part_ml, int* counters,
+                         int num_pages, float scale, int window, int chunk_mask, int n_splits, float* part_acc, float* part_ml, int* counters,
                          int max_kv, int cluster_merge, cudaStream_t stream) {
     int page_shift = -1;
     for (int b = 0; b < 31; ++b)
@@ -526,21 +528,23 @@ static int launch_decode(const void* q, int q_stride, void* out, int out_stride,
     if (n_splits < 2 || n_splits > 8) cluster_merge = 0;
     int pg_cap = 0, alone = 0;
     const int cluster = cluster_merge ? n_splits : 1;
+    // the bound on the keys a query sees, for the size of the CTA's table of pages
+    const int bound = chunk_mask > 0 && (window <= 0 || chunk_mask < window) ? chunk_mask : window;
 #define AD_LAUNCH_ARGS q, q_stride, out, out_stride, k_pages, v_pages, dec_tokens, dec_seqs, n_dec, kv_len, block_table, \
-                       bt_stride, bt_rows, NH, NKV, page_size, page_shift, pg_cap, num_pages, scale, window, n_splits, \
+                       bt_stride, bt_rows, NH, NKV, page_size, page_shift, pg_cap, num_pages, scale, window, chunk_mask, n_splits, \
                        part_acc, part_ml, counters, cluster_merge
     if (decode_grid_has_sms<D>(cluster, (long long)n_dec * NKV * n_splits, &alone)) {
-        int smem = decode_smem_bytes(D, NH / NKV, page_size, window, n_splits, max_kv, cluster_merge, AD_WARPS_ALONE, &pg_cap);
+        int smem = decode_smem_bytes(D, NH / NKV, page_size, bound, n_splits, max_kv, cluster_merge, AD_WARPS_ALONE, &pg_cap);
         if (smem < alone) smem = alone;
         int dev = 0, per_block = 0;
         cudaGetDevice(&dev);
         cudaDeviceGetAttribute(&per_block, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
         if (smem <= per_block) return launch_decode_with<D, AD_WARPS_ALONE>(AD_LAUNCH_ARGS, smem, stream);
         // too many partial results beside eight rings: four warps, still one CTA to an SM
-        smem = decode_smem_bytes(D, NH / NKV, page_size, window, n_splits, max_kv, cluster_merge, AD_WARPS, &pg_cap);
+        smem = decode_smem_bytes(D, NH / NKV, page_size, bound, n_splits, max_kv, cluster_merge, AD_WARPS, &pg_cap);
         return launch_decode_with<D, AD_WARPS>(AD_LAUNCH_ARGS, smem < alone ? alone : smem, stream);
     }
-    const int smem = decode_smem_bytes(D, NH / NKV, page_size, window, n_splits, max_kv, cluster_merge, AD_WARPS, &pg_cap);
+    const int smem = decode_smem_bytes(D, NH / NKV, page_size, bound, n_splits, max_kv, cluster_merge, AD_WARPS, &pg_cap);
     return launch_decode_with<D, AD_WARPS>(AD_LAUNCH_ARGS, smem, stream);
 #undef AD_LAUNCH_ARGS
 }
@@ -552,7 +556,7 @@ static int launch_decode(const void* q, int q_stride, void* out, int out_stride,
 ACV_API int acv_attention_decode(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,
                                  const void* v_pages, const int* dec_tokens, const int* dec_seqs, int n_dec,
                                  const int* kv_len, const int* block_table, int bt_stride, const int* bt_rows, int NH,
-                                 int NKV, int D, int page_size, int num_pages, float scale, int window, int n_splits, float* part_acc,
+                                 int NKV, int D, int page_size, int num_pages, float scale, int window, int chunk_mask, int n_splits, float* part_acc,
                                  float* part_ml, int* counters, long long scratch_floats, long long scratch_ml_floats,
                                  long long scratch_counters, int max_kv, int cluster_merge, cudaStream_t stream) {
     if (n_dec <= 0) return 0;
@@ -568,7 +572,7 @@ ACV_API int acv_attention_decode(const void* q, int q_stride, void* out, int out
         if ((uintptr_t)part_ml & 7) return ACV_ERR_ALIGN;      // (max, sum) are read as pairs
     }
 #define AD_ARGS q, q_stride, out, out_stride, k_pages, v_pages, dec_tokens, dec_seqs, n_dec, kv_len, block_table, \
-                bt_stride, bt_rows, NH, NKV, page_size, num_pages, scale, window, n_splits, part_acc, part_ml, counters, max_kv, \
+                bt_stride, bt_rows, NH, NKV, page_size, num_pages, scale, window, chunk_mask, n_splits, part_acc, part_ml, counters, max_kv, \
                 cluster_merge, stream
     switch (D) {
         case 64: return launch_decode<64>(AD_ARGS);
@@ -667,7 +671,7 @@ ACV_API int acv_attention_decode_static(const void* q, int q_stride, void* out, 
     cudaError_t e = cudaMemsetAsync(cnt, 0, (size_t)counters * sizeof(int), stream);
     if (e != cudaSuccess) return (int)e;
     return acv_attention_decode(q, q_stride, out, out_stride, k_pages, v_pages, dec_tokens, dec_seqs, n_dec, kv_len,
-                                block_table, bt_stride, nullptr, NH, NKV, D, page_size, num_pages, scale, window, n_splits,
+                                block_table, bt_stride, nullptr, NH, NKV, D, page_size, num_pages, scale, window, 0, n_splits,
                                 part_acc, part_ml, cnt, acc_floats, ml_floats, counters, max_kv, 0, stream);
 }
 

@@ -49,7 +49,7 @@ struct AttnTcParams {
     const int* block_table;
     int bt_stride;
     const int* bt_rows;         // the row of block_table of each request of the batch (null: its index)
-    int NH, NKV, page_size, page_shift, num_pages, window;
+    int NH, NKV, page_size, page_shift, num_pages, window, chunk;
     float scale;
     int* status;
 };
@@ -120,7 +120,15 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     const int rows = min(AT_BM, q_len - q0);
     const int pos0 = p.kv_len[seq] - q_len + q0;            // absolute position of the tile's first query
     const int hi = pos0 + rows - 1;                         // last key any row sees
-    const int lo = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
+    // first key that a row at position x sees: the window's lower edge and/or the start of x's chunk (chunks are
+    // counted from position 0 of the request); it grows with x, so the tile's first row gives the tile's first key
+    auto first_seen = [&](int x) {
+        int f = p.window > 0 ? max(0, x - p.window + 1) : 0;
+        if (p.chunk > 0) f = max(f, x / p.chunk * p.chunk);
+        return f;
+    };
+    const int lo = first_seen(pos0);
+    const int lo_last = first_seen(hi);                     // key tiles that begin before it need the mask
     const int j_first = lo & ~(AT_BN - 1);
     const int n_tiles = (hi - j_first) / AT_BN + 1;
     const int* bt = p.block_table + (size_t)(p.bt_rows ? p.bt_rows[seq] : seq) * p.bt_stride;
@@ -225,6 +233,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         const int wq = warp & 3;                                // the tensor-memory lanes this warp may touch
         const int r = wq * 32 + lane;                           // this thread's query row = tensor-memory lane
         const int pos = pos0 + r;
+        const int pos_lo = first_seen(pos);
         const uint32_t lane_base = (uint32_t)(wq * 32) << 16;
         const uint32_t tmem_s = tmem + hs * 128 + lane_base, tmem_o = tmem + 256 + hs * 128 + lane_base;
         const float scale_log2 = p.scale * AT_LOG2E;
@@ -243,13 +252,13 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
             TL_PHASE(0);
             const uint32_t tmem_sx = tmem_s + x * AT_HALF;
             const int j0 = j_first + t * AT_BN + x * AT_HALF;
-            const bool need_mask = j0 + AT_HALF - 1 > pos0 || (p.window > 0 && j0 <= pos0 + AT_BM - 1 - p.window);
+            const bool need_mask = j0 + AT_HALF - 1 > pos0 || j0 < lo_last;
             uint32_t ra[32], rb[32];
             auto masked = [&](uint32_t (&raw)[32], int c0) {
 #pragma unroll
                 for (int c = 0; c < 32; ++c) {
                     const int j = j0 + c0 + c;
-                    const bool seen = j <= pos && (p.window <= 0 || j > pos - p.window);
+                    const bool seen = j <= pos && j >= pos_lo;
                     raw[c] = seen ? raw[c] : 0xff800000u;       // -inf
                 }
             };
@@ -370,7 +379,8 @@ static int launch_attn_tc(const CUtensorMap& mq, const CUtensorMap& mk, const CU
 ACV_API int acv_attention_tc(const void* q, int q_stride, int T, void* out, int out_stride, const void* k_pages,
                              const void* v_pages, const int* tile_seq, const int* tile_q0, int n_tiles, const int* cu_q,
                              const int* kv_len, const int* block_table, int bt_stride, const int* bt_rows, int NH, int NKV,
-                             int D, int page_size, int num_pages, float scale, int window, int* status, cudaStream_t stream) {
+                             int D, int page_size, int num_pages, float scale, int window, int chunk, int* status,
+                             cudaStream_t stream) {
     if (n_tiles <= 0) return 0;
     if (NKV <= 0 || NH % NKV || NH > 65535 || (D != 64 && D != 128)) return ACV_ERR_SIZE;
     if ((long long)n_tiles * NH > 0x7fffffffLL) return ACV_ERR_SIZE;
@@ -393,7 +403,7 @@ ACV_API int acv_attention_tc(const void* q, int q_stride, int T, void* out, int 
     AttnTcParams p;
     p.out = (bf16*)out; p.out_stride = out_stride; p.tile_seq = tile_seq; p.tile_q0 = tile_q0; p.cu_q = cu_q;
     p.kv_len = kv_len; p.block_table = block_table; p.bt_stride = bt_stride; p.bt_rows = bt_rows; p.NH = NH; p.NKV = NKV;
-    p.page_size = page_size; p.page_shift = page_shift; p.num_pages = num_pages; p.window = window; p.scale = scale;
+    p.page_size = page_size; p.page_shift = page_shift; p.num_pages = num_pages; p.window = window; p.chunk = chunk; p.scale = scale;
     p.status = status;
     if (D == 64) return launch_attn_tc<64>(mq, mk, mv, p, n_tiles, stream);
     return launch_attn_tc<128>(mq, mk, mv, p, n_tiles, stream);

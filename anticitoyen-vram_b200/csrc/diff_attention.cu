@@ -27,8 +27,13 @@
 // ----------------------------------------------------------------------------- norm of the heads' vectors + append
 // q: [T, NQ vectors of D], k: [T, NK vectors of D] (NK / NKV vectors make one key row), v: [T, NKV rows of DV].
 // One warp per vector (q, k) or value row.  Null k skips keys and values (a layer that reads another layer's).
+// With q_out the normed query vectors do not go back in place: vector a of a head (a < per = NK / NKV) becomes a query
+// row of its own, per * D elements long, that holds the vector at offset a * D and zeros elsewhere.  Such a row's
+// product with a whole key row is the map's score, so attention kernels that know one query vector per head serve
+// the maps as 'per' times as many heads over the same key/value heads.
 template <typename T>
-__global__ void heads_norm_append_kernel(T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v, int row_stride,
+__global__ void heads_norm_append_kernel(T* __restrict__ q, T* __restrict__ q_out, int q_out_stride, const T* __restrict__ k,
+                                         const T* __restrict__ v, int row_stride,
                                          int NQ, int NK, int NKV, int D, int DV, const float* __restrict__ q_w,
                                          const float* __restrict__ k_w, float eps, const int* __restrict__ positions,
                                          const int* __restrict__ seq_of_token, const int* __restrict__ block_table,
@@ -69,7 +74,14 @@ __global__ void heads_norm_append_kernel(T* __restrict__ q, const T* __restrict_
     ss = warp_sum(ss);
     const float inv = 1.f / sqrtf(ss / (float)D + eps);
     T* dst;
-    if (is_q) {
+    if (is_q && q_out) {
+        const int per = NK / NKV;
+        T* wide = q_out + (size_t)t * q_out_stride + (size_t)vec * per * D;
+        const int a = vec % per;
+        for (int e = lane; e < per * D; e += 32)
+            if (e / D != a) wide[e] = from_f32<T>(0.f);
+        dst = wide + a * D;
+    } else if (is_q) {
         dst = q + (size_t)t * row_stride + (size_t)vec * D;
     } else {
         const int per = NK / NKV;                   // key vectors in one key row
@@ -79,22 +91,23 @@ __global__ void heads_norm_append_kernel(T* __restrict__ q, const T* __restrict_
     for (int e = lane; e < D; e += 32) dst[e] = from_f32<T>(to_f32(src[e]) * inv * (w ? w[e] : 1.f));
 }
 
-ACV_API int acv_heads_norm_append(void* q, const void* k, const void* v, int row_stride, int T_tokens, int NQ, int NK, int NKV,
+ACV_API int acv_heads_norm_append(void* q, void* q_out, int q_out_stride, const void* k, const void* v, int row_stride, int T_tokens, int NQ, int NK, int NKV,
                                   int D, int DV, const float* q_w, const float* k_w, float eps, const int* positions,
                                   const int* seq_of_token, const int* block_table, int bt_stride, const int* bt_rows,
                                   void* k_pages, void* v_pages, int page_size, int num_pages, int dtype, cudaStream_t stream) {
     if (T_tokens <= 0) return 0;
+    if (q_out && (NKV <= 0 || NK <= 0 || NK % NKV)) return ACV_ERR_SIZE;
     if (D <= 0 || NQ <= 0 || (k && (NKV <= 0 || NK % NKV || DV <= 0 || !v || !k_pages || !v_pages || !block_table)))
         return ACV_ERR_SIZE;
     const int units = NQ + (k ? NK + NKV : 0);
     dim3 grid(T_tokens, (units + DA_WARPS - 1) / DA_WARPS);
     if (dtype == ACV_F32)
-        acv_launch(PDL_ROPE, heads_norm_append_kernel<float>, grid, DA_WARPS * 32, 0, stream, (float*)q, (const float*)k,
-                   (const float*)v, row_stride, NQ, NK, NKV, D, DV, q_w, k_w, eps, positions, seq_of_token, block_table,
+        acv_launch(PDL_ROPE, heads_norm_append_kernel<float>, grid, DA_WARPS * 32, 0, stream, (float*)q, (float*)q_out, q_out_stride,
+                   (const float*)k, (const float*)v, row_stride, NQ, NK, NKV, D, DV, q_w, k_w, eps, positions, seq_of_token, block_table,
                    bt_stride, bt_rows, (float*)k_pages, (float*)v_pages, page_size, num_pages);
     else if (dtype == ACV_BF16)
-        acv_launch(PDL_ROPE, heads_norm_append_kernel<bf16>, grid, DA_WARPS * 32, 0, stream, (bf16*)q, (const bf16*)k,
-                   (const bf16*)v, row_stride, NQ, NK, NKV, D, DV, q_w, k_w, eps, positions, seq_of_token, block_table,
+        acv_launch(PDL_ROPE, heads_norm_append_kernel<bf16>, grid, DA_WARPS * 32, 0, stream, (bf16*)q, (bf16*)q_out, q_out_stride,
+                   (const bf16*)k, (const bf16*)v, row_stride, NQ, NK, NKV, D, DV, q_w, k_w, eps, positions, seq_of_token, block_table,
                    bt_stride, bt_rows, (bf16*)k_pages, (bf16*)v_pages, page_size, num_pages);
     else
         return ACV_ERR_DTYPE;
@@ -242,4 +255,58 @@ ACV_API int acv_diff_attention_generic(const void* q, int q_stride, void* out, i
                                          bt_stride, bt_rows, T_tokens, NH, NKV, D, DV, page_size, num_pages, scale, window, chunk,
                                          lambda, eps, out_scale, stream);
     return ACV_ERR_DTYPE;
+}
+
+// ----------------------------------------------------------------------------- the maps' outputs combined
+// maps: [T, NH * 2 rows of DV] (head h's map 1, then its map 2, as attention kernels with one query vector per head
+// leave them); out[t, h] = unit_rms(o1 - lambda o2) * out_scale, in 32-bit.  One warp per (token, head).
+template <typename T, int NR>
+__global__ void diff_combine_kernel(const T* __restrict__ maps, int maps_stride, T* __restrict__ out, int out_stride, int NH,
+                                    int DV, float lambda, float eps, float out_scale) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int h = blockIdx.y * DA_WARPS + warp;
+    const int t = blockIdx.x;
+    if (h >= NH) return;
+    const T* a1 = maps + (size_t)t * maps_stride + (size_t)(2 * h) * DV;
+    const T* a2 = a1 + DV;
+    float o[NR];
+    float ss = 0.f;
+#pragma unroll
+    for (int r = 0; r < NR; ++r) {
+        const int e = lane + 32 * r;
+        o[r] = e < DV ? to_f32(a1[e]) - lambda * to_f32(a2[e]) : 0.f;
+        ss += o[r] * o[r];
+    }
+    ss = warp_sum(ss);
+    const float f = out_scale / sqrtf(ss / (float)DV + eps);
+    T* orow = out + (size_t)t * out_stride + (size_t)h * DV;
+#pragma unroll
+    for (int r = 0; r < NR; ++r) {
+        const int e = lane + 32 * r;
+        if (e < DV) orow[e] = from_f32<T>(o[r] * f);
+    }
+}
+
+ACV_API int acv_diff_combine(const void* maps, int maps_stride, void* out, int out_stride, int T_tokens, int NH, int DV,
+                             float lambda, float eps, float out_scale, int dtype, cudaStream_t stream) {
+    if (T_tokens <= 0) return 0;
+    if (DV <= 0 || DV > 256 || NH <= 0) return ACV_ERR_SIZE;
+    dim3 grid(T_tokens, (NH + DA_WARPS - 1) / DA_WARPS);
+    const int nr = (DV + 31) / 32;
+#define DC_CASE(TT, N)                                                                                                  \
+    case N:                                                                                                             \
+        acv_launch(PDL_ATTN, diff_combine_kernel<TT, N>, grid, DA_WARPS * 32, 0, stream, (const TT*)maps, maps_stride,  \
+                   (TT*)out, out_stride, NH, DV, lambda, eps, out_scale);                                               \
+        break;
+    if (dtype == ACV_F32) {
+        switch (nr) { DC_CASE(float, 1) DC_CASE(float, 2) DC_CASE(float, 3) DC_CASE(float, 4) DC_CASE(float, 5) DC_CASE(float, 6) DC_CASE(float, 7) DC_CASE(float, 8) }
+    } else if (dtype == ACV_BF16) {
+        switch (nr) { DC_CASE(bf16, 1) DC_CASE(bf16, 2) DC_CASE(bf16, 3) DC_CASE(bf16, 4) DC_CASE(bf16, 5) DC_CASE(bf16, 6) DC_CASE(bf16, 7) DC_CASE(bf16, 8) }
+    } else {
+        return ACV_ERR_DTYPE;
+    }
+#undef DC_CASE
+    return acv_launch_status();
 }

@@ -74,14 +74,15 @@ def _declare(lib: ctypes.CDLL) -> None:
         "acv_gemm_simt": [P, I, P, I, P, I, I, I, I, I, I, P],
         "acv_gemm_tc_qkv": [P, I, P, I, P, I, I, I, I, I, I, I, P, LL, P, LL, P, I, I, I, I, I, I, P, P, F, P, I, P, P, P, I, P, P, P, I, I, P],
         "acv_gemm_tc": [P, I, P, I, P, I, I, I, I, I, I, I, I, I, P, LL, P, LL, P, I, I, I, P],
-        "acv_attention_decode": [P, I, P, I, P, P, P, P, I, P, P, I, P, I, I, I, I, I, F, I, I, P, P, P, LL, LL, LL, I, I, P],
-        "acv_attention_tc": [P, I, I, P, I, P, P, P, P, I, P, P, P, I, P, I, I, I, I, I, F, I, P, P],
-        "acv_attention_chunk": [P, I, P, I, P, P, P, P, I, P, P, P, I, P, I, I, I, I, I, F, I, I, P],
+        "acv_attention_decode": [P, I, P, I, P, P, P, P, I, P, P, I, P, I, I, I, I, I, F, I, I, I, P, P, P, LL, LL, LL, I, I, P],
+        "acv_attention_tc": [P, I, I, P, I, P, P, P, P, I, P, P, P, I, P, I, I, I, I, I, F, I, I, P, P],
+        "acv_attention_chunk": [P, I, P, I, P, P, P, P, I, P, P, P, I, P, I, I, I, I, I, F, I, I, I, P],
         "acv_table_update": [P, I, I, P, I, P],
         "acv_embed_scaled": [P, P, P, I, I, I, F, I, P],
         "acv_add_rmsnorm_f32": [P, P, P, P, P, I, I, F, I, P],
         "acv_scale_f32": [P, LL, F, P],
-        "acv_heads_norm_append": [P, P, P, I, I, I, I, I, I, I, P, P, F, P, P, P, I, P, P, P, I, I, I, P],
+        "acv_heads_norm_append": [P, P, I, P, P, I, I, I, I, I, I, I, P, P, F, P, P, P, I, P, P, P, I, I, I, P],
+        "acv_diff_combine": [P, I, P, I, I, I, I, F, F, F, I, P],
         "acv_diff_attention_generic": [P, I, P, I, P, P, P, P, P, I, P, I, I, I, I, I, I, I, F, I, I, F, F, F, I, P],
         "acv_moe_route": [P, I, P, P, I, I, I, I, I, I, P, P, P, I, P],
         "acv_moe_group": [P, I, I, I, P, P, P, P],
@@ -687,7 +688,7 @@ def attention_decode(q: torch.Tensor, out: torch.Tensor, k_pages: torch.Tensor, 
                      dec_tokens: torch.Tensor, dec_seqs: torch.Tensor, n_dec: int, kv_len: torch.Tensor,
                      block_table: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int, scale: float,
                      window: int, n_splits: int, max_kv: int = 0, cluster_merge: bool = True,
-                     table_rows: torch.Tensor | None = None) -> torch.Tensor:
+                     table_rows: torch.Tensor | None = None, chunk: int = 0) -> torch.Tensor:
     """Attention of requests that bring one token each, over their pages, split over the context.
 
     Up to 8 splits are merged inside a thread-block cluster (through its shared memory); more, or
@@ -699,7 +700,7 @@ def attention_decode(q: torch.Tensor, out: torch.Tensor, k_pages: torch.Tensor, 
     _check(library().acv_attention_decode(
         _p(q), q.stride(0), _p(out), out.stride(0), _p(k_pages), _p(v_pages), _p(dec_tokens), _p(dec_seqs), n_dec,
         _p(kv_len), _p(block_table), block_table.stride(0), _p(table_rows), num_heads, num_kv_heads, head_dim,
-        k_pages.shape[2], k_pages.shape[0], scale, window, n_splits, _p(acc), _p(ml), _p(cnt), acc.numel(), ml.numel(), cnt.numel(),
+        k_pages.shape[2], k_pages.shape[0], scale, window, chunk, n_splits, _p(acc), _p(ml), _p(cnt), acc.numel(), ml.numel(), cnt.numel(),
         max_kv or block_table.shape[1] * k_pages.shape[2], 1 if use_cluster else 0, _stream()), "attention_decode")
     return out
 
@@ -707,12 +708,13 @@ def attention_decode(q: torch.Tensor, out: torch.Tensor, k_pages: torch.Tensor, 
 def attention_chunk(q: torch.Tensor, out: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
                     tile_seq: torch.Tensor, tile_q0: torch.Tensor, n_tiles: int, cu_q: torch.Tensor,
                     kv_len: torch.Tensor, block_table: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int,
-                    scale: float, window: int, table_rows: torch.Tensor | None = None, max_kv: int = 0) -> torch.Tensor:
+                    scale: float, window: int, table_rows: torch.Tensor | None = None, max_kv: int = 0,
+                    chunk: int = 0) -> torch.Tensor:
     """Causal attention of portions of prompts (tiles of QUERY_TILE query tokens) over their requests' pages."""
     _check(library().acv_attention_chunk(
         _p(q), q.stride(0), _p(out), out.stride(0), _p(k_pages), _p(v_pages), _p(tile_seq), _p(tile_q0), n_tiles,
         _p(cu_q), _p(kv_len), _p(block_table), block_table.stride(0), _p(table_rows), num_heads, num_kv_heads, head_dim,
-        k_pages.shape[2], k_pages.shape[0], scale, window, max_kv or block_table.shape[1] * k_pages.shape[2], _stream()),
+        k_pages.shape[2], k_pages.shape[0], scale, window, chunk, max_kv or block_table.shape[1] * k_pages.shape[2], _stream()),
         "attention_chunk")
     return out
 
@@ -720,13 +722,13 @@ def attention_chunk(q: torch.Tensor, out: torch.Tensor, k_pages: torch.Tensor, v
 def attention_tc(q: torch.Tensor, out: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
                  tile_seq: torch.Tensor, tile_q0: torch.Tensor, n_tiles: int, cu_q: torch.Tensor, kv_len: torch.Tensor,
                  block_table: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int, scale: float,
-                 window: int, table_rows: torch.Tensor | None = None) -> torch.Tensor:
+                 window: int, table_rows: torch.Tensor | None = None, chunk: int = 0) -> torch.Tensor:
     """Causal attention of portions of prompts on tcgen05 (tiles of QUERY_TILE query tokens, pages by TMA)."""
     _, _, status = _gemm_buffers(q.device, 0, 0)
     _check(library().acv_attention_tc(
         _p(q), q.stride(0), q.shape[0], _p(out), out.stride(0), _p(k_pages), _p(v_pages), _p(tile_seq), _p(tile_q0),
         n_tiles, _p(cu_q), _p(kv_len), _p(block_table), block_table.stride(0), _p(table_rows), num_heads, num_kv_heads,
-        head_dim, k_pages.shape[2], k_pages.shape[0], scale, window, _p(status), _stream()), "attention_tc")
+        head_dim, k_pages.shape[2], k_pages.shape[0], scale, window, chunk, _p(status), _stream()), "attention_tc")
     return out
 
 
@@ -782,8 +784,10 @@ def attention_work_decode(padded: int, max_kv: int) -> tuple[dict, dict]:
 
 def attention(qkv: torch.Tensor, out: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, ctx,
               block_table: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int, scale: float,
-              window: int = 0, work: dict | None = None) -> torch.Tensor:
-    """Attention of every token of the step over its request's pages.
+              window: int = 0, work: dict | None = None, chunk: int = 0) -> torch.Tensor:
+    """Attention of every token of the step over its request's pages.  A query sees the keys at or before its
+    position; with ``window`` > 0 the last ``window`` of them; with ``chunk`` > 0 those of its own chunk of ``chunk``
+    positions counted from the request's position 0.
 
     ``qkv`` is the stacked projection after norm and rotation (queries are its first
     num_heads*head_dim columns); ``ctx`` is the step's StepContext; ``work`` the step's work lists
@@ -792,23 +796,26 @@ def attention(qkv: torch.Tensor, out: torch.Tensor, k_pages: torch.Tensor, v_pag
     one; everything else to the generic kernel."""
     rows = getattr(ctx, "table_rows", None)
     if not tensor_core_attention_takes(qkv.dtype, num_heads, num_kv_heads, head_dim):
+        if chunk > 0:
+            raise KernelError("attention: the chunked mask is built for the tensor-core kernels' sizes only")
         return attention_generic(qkv, out, k_pages, v_pages, ctx.positions, ctx.seq_of_token, block_table, num_heads,
                                  num_kv_heads, head_dim, scale, window, table_rows=rows)
     w = work if work is not None else ctx.work
     if w["n_dec"]:
         kv = min(w["max_dec_kv"], window) if window > 0 else w["max_dec_kv"]
+        kv = min(kv, chunk) if chunk > 0 else kv
         n_splits, in_clusters = (w["n_splits"], True) if w.get("n_splits") else \
             decode_plan(w["n_dec"], num_heads, num_kv_heads, head_dim, k_pages.shape[2], kv)
         attention_decode(qkv, out, k_pages, v_pages, w["dec_tokens"], w["dec_seqs"], w["n_dec"], ctx.kv_len,
                          block_table, num_heads, num_kv_heads, head_dim, scale, window, n_splits, w["max_dec_kv"],
-                         cluster_merge=in_clusters, table_rows=rows)
+                         cluster_merge=in_clusters, table_rows=rows, chunk=chunk)
     if w["n_tiles"] and attention_tc_takes(qkv, out, k_pages, head_dim):
         attention_tc(qkv, out, k_pages, v_pages, w["tile_seq"], w["tile_q0"], w["n_tiles"], ctx.cu_q, ctx.kv_len,
-                     block_table, num_heads, num_kv_heads, head_dim, scale, window, table_rows=rows)
+                     block_table, num_heads, num_kv_heads, head_dim, scale, window, table_rows=rows, chunk=chunk)
     elif w["n_tiles"]:
         attention_chunk(qkv, out, k_pages, v_pages, w["tile_seq"], w["tile_q0"], w["n_tiles"], ctx.cu_q, ctx.kv_len,
                         block_table, num_heads, num_kv_heads, head_dim, scale, window, table_rows=rows,
-                        max_kv=w.get("max_tile_kv", 0))
+                        max_kv=w.get("max_tile_kv", 0), chunk=chunk)
     return out
 
 
@@ -940,11 +947,14 @@ def scale_f32(x: torch.Tensor, s: float) -> torch.Tensor:
 def heads_norm_append(qkv: torch.Tensor, num_q_vectors: int, num_k_vectors: int, num_kv_heads: int, dim: int, value_dim: int,
                       q_weight: torch.Tensor | None, k_weight: torch.Tensor | None, eps: float, positions: torch.Tensor,
                       seq_of_token: torch.Tensor, block_table: torch.Tensor | None, k_pages: torch.Tensor | None,
-                      v_pages: torch.Tensor | None, table_rows: torch.Tensor | None = None) -> None:
+                      v_pages: torch.Tensor | None, table_rows: torch.Tensor | None = None,
+                      q_out: torch.Tensor | None = None) -> None:
     """RMS norm of each of the ``num_q_vectors`` query vectors of ``dim`` elements at the head of a row of ``qkv``
     (in place) and, when pages are given, of the ``num_k_vectors`` key vectors behind them (written into the key
     pages, ``num_k_vectors / num_kv_heads`` vectors to a key row) and the copy of the ``num_kv_heads`` value rows of
-    ``value_dim`` elements behind those into the value pages.  Without pages the row holds queries only."""
+    ``value_dim`` elements behind those into the value pages.  Without pages the row holds queries only.
+    ``q_out`` [T, num_q_vectors * key row]: the normed query vectors go there instead, each as a row as long as a key
+    row with the vector at its map's offset and zeros elsewhere (queries for kernels that know one vector per head)."""
     _need_cuda(qkv)
     T = qkv.shape[0]
     keeps = k_pages is not None
@@ -952,7 +962,7 @@ def heads_norm_append(qkv: torch.Tensor, num_q_vectors: int, num_k_vectors: int,
     k = qkv[:, q_width:] if keeps else None
     v = qkv[:, q_width + num_k_vectors * dim:] if keeps else None
     _check(library().acv_heads_norm_append(
-        _p(qkv), _p(k), _p(v), qkv.stride(0), T, num_q_vectors, num_k_vectors, num_kv_heads, dim, value_dim,
+        _p(qkv), _p(q_out), q_out.stride(0) if q_out is not None else 0, _p(k), _p(v), qkv.stride(0), T, num_q_vectors, num_k_vectors, num_kv_heads, dim, value_dim,
         _p(q_weight), _p(k_weight), eps, _p(positions), _p(seq_of_token), _p(block_table),
         block_table.stride(0) if block_table is not None else 0, _p(table_rows), _p(k_pages), _p(v_pages),
         k_pages.shape[2] if keeps else 1, k_pages.shape[0] if keeps else 0, dtype_code(qkv.dtype), _stream()),
@@ -984,6 +994,21 @@ def diff_attention(qkv: torch.Tensor, out: torch.Tensor, k_pages: torch.Tensor, 
     rows = getattr(ctx, "table_rows", None)
     return diff_attention_generic(qkv, out, k_pages, v_pages, ctx.positions, ctx.seq_of_token, block_table, num_heads,
                                   num_kv_heads, dim, value_dim, scale, lam, eps, out_scale, window, chunk, table_rows=rows)
+
+
+def diff_attention_as_heads_takes(dtype: torch.dtype, num_heads: int, num_kv_heads: int, dim: int, value_dim: int) -> bool:
+    """Whether the two maps can run as twice as many heads of the tensor-core attention kernels: key rows and value
+    rows of one size that those kernels take (each map's query padded with zeros to a key row)."""
+    return value_dim == 2 * dim and tensor_core_attention_takes(dtype, 2 * num_heads, num_kv_heads, 2 * dim)
+
+
+def diff_combine(maps: torch.Tensor, out: torch.Tensor, num_heads: int, value_dim: int, lam: float, eps: float,
+                 out_scale: float) -> torch.Tensor:
+    """out[t, h] = unit_rms(maps[t, 2h] - lam * maps[t, 2h + 1]) * out_scale over the head's ``value_dim`` values."""
+    _need_cuda(maps, out)
+    _check(library().acv_diff_combine(_p(maps), maps.stride(0), _p(out), out.stride(0), maps.shape[0], num_heads, value_dim,
+                                      lam, eps, out_scale, dtype_code(out.dtype), _stream()), "diff_combine")
+    return out
 
 
 # ----------------------------------------------------------------------------- mixture of experts

@@ -260,12 +260,25 @@ class DiffAttention(Mixer):
         table = ctx.block_tables[cache.group]
         rows = ctx.table_rows
         qkv = self.qkv(h)
+        T = qkv.shape[0]
         eps = self.norm_eps if self.norm_eps is not None else 0.0
-        if self.norm_eps is not None or self.own_kv:
+        pages = (table, cache.k_pages, cache.v_pages) if self.own_kv else (None, None, None)
+        out = torch.empty((T, NH * DV), device=h.device, dtype=h.dtype)
+        work = ctx.work.get(self.metadata_key)
+        if work is not None and ops.diff_attention_as_heads_takes(h.dtype, NH, NKV, D, DV):
+            # key and value rows of one size that the tensor-core attention kernels take: each map runs as a head of its
+            # own (its query vector padded with zeros to a key row) on the prompt and decode kernels of plain attention,
+            # under the same mask; a small kernel then combines the two maps of every head
+            wide = torch.empty((T, 2 * NH * 2 * D), device=h.device, dtype=h.dtype)
             ops.heads_norm_append(qkv, 2 * NH, 2 * NKV, NKV, D, DV, self.q_norm, self.k_norm, eps, ctx.positions,
-                                  ctx.seq_of_token, table if self.own_kv else None, cache.k_pages if self.own_kv else None,
-                                  cache.v_pages if self.own_kv else None, table_rows=rows)
-        out = torch.empty((qkv.shape[0], NH * DV), device=h.device, dtype=h.dtype)
+                                  ctx.seq_of_token, *pages, table_rows=rows, q_out=wide)
+            maps = torch.empty((T, 2 * NH * DV), device=h.device, dtype=h.dtype)
+            ops.attention(wide, maps, cache.k_pages, cache.v_pages, ctx, table, 2 * NH, NKV, 2 * D, self.scale, self.window,
+                          work=work, chunk=self.chunk)
+            ops.diff_combine(maps, out, NH, DV, self.lam, eps, 1.0 - self.diff)
+            return self.o(out)
+        ops.heads_norm_append(qkv, 2 * NH, 2 * NKV, NKV, D, DV, self.q_norm, self.k_norm, eps, ctx.positions,
+                              ctx.seq_of_token, *pages, table_rows=rows)
         ops.diff_attention(qkv, out, cache.k_pages, cache.v_pages, ctx, table, NH, NKV, D, DV, self.scale, self.lam, eps,
-                           1.0 - self.diff, self.window, self.chunk, work=ctx.work.get(self.metadata_key))
+                           1.0 - self.diff, self.window, self.chunk, work=work)
         return self.o(out)
