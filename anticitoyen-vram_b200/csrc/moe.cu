@@ -15,6 +15,7 @@
 //   acv_moe_combine  per token: the chosen experts' outputs in the order of the choice, plus the
 //                    shared expert's output times its gate, summed in 32-bit
 #include "common.cuh"
+#include "mma_tiles.cuh"
 
 #define MOE_TILE 64          // rows of a tile of the grouped products (ops.MOE_TILE)
 
@@ -284,6 +285,149 @@ ACV_API int acv_moe_gemm_simt(const void* A, int lda, const void* W, long long w
         return ACV_ERR_DTYPE;
     }
 #undef MG_LAUNCH
+    return acv_launch_status();
+}
+
+// ----------------------------------------------------------------------------- grouped products on the tensor cores
+// bfloat16, mma.sync m16n8k16 with float accumulators.  A CTA of four warps owns a tile of MOE_TILE grouped rows x 64
+// output columns (with GLU: 64 gate and the 64 up columns of the same numbers); a warp owns 16 rows.  Operands come in
+// slabs of 64 k through two stages of 16-byte asynchronous copies into swizzled tiles: the rows of A gathered by the
+// grouping (rows without a token are zero-filled), the expert's weight rows by the tile's expert.  Same epilogues as
+// the CUDA-core form: the row's weight times the accumulators, then the activation (GLU), or float output (down).
+// Rows of 16-byte alignment are needed: K, lda, ldw and the experts' stride multiples of 8.
+#define MM_BN 64
+#define MM_BK 64
+#define MM_THREADS 128
+
+template <bool GLU>
+__global__ void __launch_bounds__(MM_THREADS)
+moe_gemm_mma_kernel(const bf16* __restrict__ A, int lda, const bf16* __restrict__ W, long long w_expert_stride, int ldw,
+                    void* __restrict__ C, int ldc, const int* __restrict__ grouped, const int* __restrict__ tile_expert,
+                    const float* __restrict__ row_weight, int top, int N, int K, float limit, float alpha) {
+    extern __shared__ __align__(128) unsigned char mm_smem[];
+    constexpr int A_BYTES = MOE_TILE * MM_BK * 2;
+    constexpr int W_BYTES = MM_BN * MM_BK * 2;
+    constexpr int STAGE = A_BYTES + (GLU ? 2 : 1) * W_BYTES;
+    __shared__ int src[MOE_TILE];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int tile = blockIdx.y;
+    const int expert = tile_expert[tile];
+    if (expert < 0) return;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int n0 = blockIdx.x * MM_BN;
+    if (tid < MOE_TILE) src[tid] = grouped[tile * MOE_TILE + tid];
+    __syncthreads();
+    const bf16* We = W + (size_t)expert * w_expert_stride;
+
+    auto load = [&](int kb, int stage) {
+        unsigned char* base = mm_smem + stage * STAGE;
+        const int k0 = kb * MM_BK;
+#pragma unroll
+        for (int it = 0; it < MOE_TILE * 8 / MM_THREADS; ++it) {
+            const int id = tid + it * MM_THREADS;
+            const int r = id >> 3, c = id & 7;
+            const int s = src[r];
+            const long long arow = GLU ? (s >= 0 ? s / top : -1) : (s >= 0 ? (long long)tile * MOE_TILE + r : -1);
+            const bool ok = arow >= 0 && k0 + c * 8 < K;
+            cp_async16(smem_u32(base + tile_off<MM_BK>(r, c)), ok ? (const void*)(A + arow * lda + k0 + c * 8) : (const void*)A, ok);
+        }
+#pragma unroll
+        for (int it = 0; it < MM_BN * 8 / MM_THREADS; ++it) {
+            const int id = tid + it * MM_THREADS;
+            const int r = id >> 3, c = id & 7;
+            const int n = n0 + r;
+            const bool ok = n < N && k0 + c * 8 < K;
+            cp_async16(smem_u32(base + A_BYTES + tile_off<MM_BK>(r, c)),
+                       ok ? (const void*)(We + (size_t)n * ldw + k0 + c * 8) : (const void*)We, ok);
+            if constexpr (GLU)
+                cp_async16(smem_u32(base + A_BYTES + W_BYTES + tile_off<MM_BK>(r, c)),
+                           ok ? (const void*)(We + (size_t)(N + n) * ldw + k0 + c * 8) : (const void*)We, ok);
+        }
+    };
+
+    float acc[MM_BN / 8][4], acu[GLU ? MM_BN / 8 : 1][4];
+#pragma unroll
+    for (int i = 0; i < MM_BN / 8; ++i)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            acc[i][e] = 0.f;
+            if constexpr (GLU) acu[i][e] = 0.f;
+        }
+    const int nkb = (K + MM_BK - 1) / MM_BK;
+    const int mi = lane >> 3, lr = lane & 7;
+    load(0, 0);
+    cp_async_commit();
+    for (int kb = 0; kb < nkb; ++kb) {
+        const int stage = kb & 1;
+        if (kb + 1 < nkb) load(kb + 1, stage ^ 1);
+        cp_async_commit();
+        cp_async_wait<1>();
+        __syncthreads();
+        const uint32_t ab = smem_u32(mm_smem + stage * STAGE), wb = ab + A_BYTES;
+#pragma unroll
+        for (int kd = 0; kd < MM_BK / 16; ++kd) {
+            uint32_t af[4];
+            ldmatrix_x4(af, ab + tile_off<MM_BK>(warp * 16 + (mi & 1) * 8 + lr, kd * 2 + (mi >> 1)));
+#pragma unroll
+            for (int np = 0; np < MM_BN / 16; ++np) {
+                uint32_t b[4];
+                ldmatrix_x4(b, wb + tile_off<MM_BK>(np * 16 + (mi >> 1) * 8 + lr, kd * 2 + (mi & 1)));
+                mma_bf16(acc[2 * np], af, b[0], b[1]);
+                mma_bf16(acc[2 * np + 1], af, b[2], b[3]);
+                if constexpr (GLU) {
+                    ldmatrix_x4(b, wb + W_BYTES + tile_off<MM_BK>(np * 16 + (mi >> 1) * 8 + lr, kd * 2 + (mi & 1)));
+                    mma_bf16(acu[2 * np], af, b[0], b[1]);
+                    mma_bf16(acu[2 * np + 1], af, b[2], b[3]);
+                }
+            }
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+        const int r = warp * 16 + (lane >> 2) + half * 8;
+        const int s = src[r];
+        if (s < 0) continue;
+        const float w = row_weight ? row_weight[s] : 1.f;
+        const size_t crow = (size_t)(tile * MOE_TILE + r) * ldc;
+#pragma unroll
+        for (int nt = 0; nt < MM_BN / 8; ++nt) {
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const int col = n0 + nt * 8 + (lane & 3) * 2 + e;
+                if (col >= N) continue;
+                const float v = acc[nt][half * 2 + e] * w;
+                if constexpr (GLU)
+                    ((bf16*)C)[crow + col] = __float2bfloat16_rn(glu_act<bf16>(v, acu[nt][half * 2 + e] * w, limit, alpha));
+                else
+                    ((float*)C)[crow + col] = v;
+            }
+        }
+    }
+}
+
+// which: 0 = gate/up with activation (C bfloat16), 1 = down (C float)
+ACV_API int acv_moe_gemm_mma(const void* A, int lda, const void* W, long long w_expert_stride, int ldw, void* C, int ldc,
+                             const int* grouped, const int* tile_expert, const float* row_weight, int top, int max_tiles,
+                             int N, int K, int which, float limit, float alpha, cudaStream_t stream) {
+    if (max_tiles <= 0 || N <= 0) return 0;
+    if (K <= 0 || top <= 0 || max_tiles > 65535) return ACV_ERR_SIZE;
+    if ((K % 8) || (lda % 8) || (ldw % 8) || (w_expert_stride % 8) || ((uintptr_t)A & 15) || ((uintptr_t)W & 15)) return ACV_ERR_ALIGN;
+    dim3 grid((N + MM_BN - 1) / MM_BN, max_tiles);
+    if (which == 0) {
+        const int smem = 2 * (MOE_TILE * MM_BK * 2 + 2 * MM_BN * MM_BK * 2);
+        static AcvSmemConfig cfg;
+        if (int rc = acv_ensure_smem(cfg, moe_gemm_mma_kernel<true>, smem)) return rc;
+        acv_launch(PDL_GEMM, moe_gemm_mma_kernel<true>, grid, MM_THREADS, smem, stream, (const bf16*)A, lda, (const bf16*)W,
+                   w_expert_stride, ldw, C, ldc, grouped, tile_expert, row_weight, top, N, K, limit, alpha);
+    } else {
+        const int smem = 2 * (MOE_TILE * MM_BK * 2 + MM_BN * MM_BK * 2);
+        static AcvSmemConfig cfg;
+        if (int rc = acv_ensure_smem(cfg, moe_gemm_mma_kernel<false>, smem)) return rc;
+        acv_launch(PDL_GEMM, moe_gemm_mma_kernel<false>, grid, MM_THREADS, smem, stream, (const bf16*)A, lda, (const bf16*)W,
+                   w_expert_stride, ldw, C, ldc, grouped, tile_expert, row_weight, top, N, K, limit, alpha);
+    }
     return acv_launch_status();
 }
 

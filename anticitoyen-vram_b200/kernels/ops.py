@@ -87,6 +87,7 @@ def _declare(lib: ctypes.CDLL) -> None:
         "acv_moe_route": [P, I, P, P, I, I, I, I, I, I, P, P, P, I, P],
         "acv_moe_group": [P, I, I, I, P, P, P, P],
         "acv_moe_gemm_simt": [P, I, P, LL, I, P, I, P, P, P, I, I, I, I, I, F, F, I, P],
+        "acv_moe_gemm_mma": [P, I, P, LL, I, P, I, P, P, P, I, I, I, I, I, F, F, P],
         "acv_moe_combine": [P, I, P, I, P, I, P, P, I, I, I, I, P],
         "acv_glu": [P, I, P, I, I, I, I, F, F, I, P],
         "acv_argmax": [P, I, I, I, P, P],
@@ -1060,15 +1061,40 @@ def moe_gemm_simt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, grouped: 
     return out
 
 
+def moe_gemm_mma_takes(a: torch.Tensor, w: torch.Tensor) -> bool:
+    """The tensor-core form of the grouped products wants bfloat16 and rows of 16-byte alignment."""
+    return (a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and a.shape[1] % 8 == 0 and a.stride(0) % 8 == 0
+            and a.stride(1) == 1 and w.is_contiguous() and (w.shape[1] * w.shape[2]) % 8 == 0 and a.data_ptr() % 16 == 0
+            and w.data_ptr() % 16 == 0)
+
+
+def moe_gemm_mma(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, grouped: torch.Tensor, tile_expert: torch.Tensor,
+                 row_weight: torch.Tensor | None, top: int, glu: bool, limit: float = 0.0, alpha: float = 0.0) -> torch.Tensor:
+    """``moe_gemm_simt`` on the tensor cores (bfloat16 operands, float accumulators; the same arguments)."""
+    _need_cuda(a, w, out, grouped, tile_expert)
+    E, NW, K = w.shape
+    N = NW // 2 if glu else NW
+    if a.shape[1] != K or out.shape[1] != N or out.stride(1) != 1 or out.dtype != (torch.bfloat16 if glu else torch.float32):
+        raise KernelError(f"moe_gemm_mma: shapes {tuple(a.shape)} x {tuple(w.shape)} -> {tuple(out.shape)} do not fit")
+    _check(library().acv_moe_gemm_mma(_p(a), a.stride(0), _p(w), w.stride(0), w.stride(1), _p(out), out.stride(0),
+                                      _p(grouped), _p(tile_expert), _p(row_weight), top, tile_expert.numel(), N, K,
+                                      0 if glu else 1, limit, alpha, _stream()), "moe_gemm_mma")
+    return out
+
+
 def moe_experts_up(h: torch.Tensor, gate_up: torch.Tensor, act: torch.Tensor, grouped: torch.Tensor, tile_expert: torch.Tensor,
                    row_weight: torch.Tensor | None, top: int, limit: float, alpha: float) -> torch.Tensor:
     """act[grouped row] = gated activation of the row's expert's gate and up products of its token; dispatch by shape."""
+    if moe_gemm_mma_takes(h, gate_up):
+        return moe_gemm_mma(h, gate_up, act, grouped, tile_expert, row_weight, top, True, limit, alpha)
     return moe_gemm_simt(h, gate_up, act, grouped, tile_expert, row_weight, top, True, limit, alpha)
 
 
 def moe_experts_down(act: torch.Tensor, down: torch.Tensor, out: torch.Tensor, grouped: torch.Tensor, tile_expert: torch.Tensor,
                      row_weight: torch.Tensor | None, top: int) -> torch.Tensor:
     """out[grouped row] (float32) = the row's expert's down product of its activations; dispatch by shape."""
+    if moe_gemm_mma_takes(act, down):
+        return moe_gemm_mma(act, down, out, grouped, tile_expert, row_weight, top, False)
     return moe_gemm_simt(act, down, out, grouped, tile_expert, row_weight, top, False)
 
 
