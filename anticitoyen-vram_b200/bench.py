@@ -217,6 +217,63 @@ def time_prefill(runner, tokens: int, reps: int = 3, warmup: int = 1) -> dict:
     return {"ms": ms, "tokens": tokens, "tokens_per_s": tokens * 1000.0 / ms, "spread_ms": max(times) - min(times)}
 
 
+def time_parts(runner, q_lens: list, kv_lens: list, reps: int = 5, layer: int = 0) -> dict:
+    """Device time of one layer's mixer and feed-forward alone, for a step in which request i brings ``q_lens[i]``
+    tokens and holds ``kv_lens[i]`` after it: median of ``reps`` runs, the L2 flushed before each (a buffer larger
+    than it is written).  Beside each time what the part has to compute and read, as the part itself reports it."""
+    model, dev = runner.model, runner.rt.device
+    vocab = model.plan.vocab_size
+    names = [f"part-{i}" for i in range(len(q_lens))]
+    entries = []
+    for i, (name, q, kv) in enumerate(zip(names, q_lens, kv_lens)):
+        ids = synthetic_ids(vocab, kv, 300 + i)
+        for pos in range(0, kv - q, 2048):
+            runner.step([StepEntry(name, ids[pos:min(pos + 2048, kv - q)], ())])
+        entries.append(StepEntry(name, ids[kv - q:], ()))
+    ctx = runner.prepare(entries)
+    entry = model.plan.schedule[layer]
+    block = model.blocks[entry.layer]
+    k_pages, v_pages = runner.storage.pages(entry.cache)
+    from .parts import CacheView
+    view = CacheView(runner.manager.plan.group_of_slot[entry.cache], entry.writes, k_pages=k_pages, v_pages=v_pages)
+    T = sum(q_lens)
+    h = (torch.randn((T, model.plan.hidden_size), device=dev) * 0.5).to(runner.rt.dtype)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+
+    def timed(fn) -> float:
+        times = []
+        for k in range(reps + 2):
+            flush.zero_()
+            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            fn()
+            end.record()
+            torch.cuda.synchronize(dev)
+            if k >= 2:
+                times.append(start.elapsed_time(end))
+        return statistics.median(times)
+
+    out = {}
+    try:
+        mixer, ff = block.mixer, block.feed_forward
+        ms = timed(lambda: mixer.forward(h, ctx, view))
+        itemsize = runner.rt.dtype.itemsize
+        out["mixer"] = {"ms": ms, "flops": mixer.flops(T) + mixer.mixing_flops(q_lens, kv_lens),
+                        "bytes": mixer.weight_bytes() + mixer.cache_bytes_read(q_lens, kv_lens, itemsize)}
+        if ff is not None:
+            ms = timed(lambda: ff.forward(h, ctx))
+            wb = ff.step_weight_bytes(T) if hasattr(ff, "step_weight_bytes") else ff.weight_bytes()
+            out["feed_forward"] = {"ms": ms, "flops": ff.flops(T), "bytes": wb}
+    finally:
+        for name in names:
+            runner.release(name)
+    code = ops.gemm_status()
+    if code:
+        ops.reset_after_failure()
+        raise Refused(f"a kernel gave up a bounded wait during the timed parts (status {code})")
+    return out
+
+
 def bench_decode(model, random_weights=False, seed=0, dtype="bfloat16", batches=(1,), context=128, n_tokens=256,
                  device="cuda:0", cuda_graphs=True, repetitions=3, prefill=0) -> dict:
     """``acvram bench --what decode``: median decode tokens/s for each batch size, with the spread; with

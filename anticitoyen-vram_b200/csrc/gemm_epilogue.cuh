@@ -16,6 +16,15 @@ struct GemmParams {
     int swap;               // 0: A = x (rows = tokens), 1: A = weight (rows = features)
     int out_f32;
     int act;                // 1: output features come in (gate, up) pairs and C[:, n/2] = silu(gate) * up
+                            // 2: the same pairs through a clamped gated unit, scaled by the row first (tokens on rows only):
+                            //    g = min(w gate, limit), u = clamp(w up, +-limit), C = g * sigmoid(alpha g) * (u + 1)
+    const float* row_scale; // act 2: w of each row of A (null: 1)
+    float glu_limit, glu_alpha;
+    // grouped product (tokens on rows): tile ta of A multiplies the rows [tile_expert[ta] * N, +N) of the B operand,
+    // which stacks `experts` matrices of N rows; only the first *tiles_used tiles of A exist
+    const int* tile_expert;
+    const int* tiles_used;
+    int experts;
     int tiles_a, tiles_b, splits, kb_per_split, n_kb;
     int group_a;            // rows of tiles that are walked together (see gt_tile_of)
     int early_w;            // 1: the weights were written long before this launch: their first tiles are loaded before the predecessor ends
@@ -58,6 +67,13 @@ __device__ __forceinline__ bf16 swiglu_pair(float gate, float up) {
     return __float2bfloat16_rn(s * u);
 }
 
+// The clamped gated unit of act 2, in float, rounded once.
+__device__ __forceinline__ bf16 glu_clamped_pair(float gate, float up, float w, float limit, float alpha) {
+    const float g = fminf(gate * w, limit);
+    const float u = fminf(fmaxf(up * w, -limit), limit);
+    return __float2bfloat16_rn(g * __fdividef(1.f, 1.f + __expf(-alpha * g)) * (u + 1.f));
+}
+
 // Swapped roles: features lie on lanes, an even lane holds the gate of 16 tokens and the next lane their up.  The two
 // share the work: each sends the other the eight values that it does not need, the even lane makes the tokens 0..7,
 // the odd lane the tokens 8..15 (all exchanges first, then the arithmetic, so that the eight chains run side by
@@ -88,8 +104,14 @@ __device__ __forceinline__ void gt_store16(const GemmParams& p, int row_a, int c
         } else if (row_a < p.M) {   // features lie on columns: (v[0], v[1]), (v[2], v[3]) ...
             bf16* dst = (bf16*)p.C + (size_t)row_a * p.ldc + (col0 >> 1);
             bf16 o[8];
+            if (p.act == 2) {
+                const float w = p.row_scale ? p.row_scale[row_a] : 1.f;
 #pragma unroll
-            for (int k = 0; k < 8; ++k) o[k] = swiglu_pair(v[2 * k], v[2 * k + 1]);
+                for (int k = 0; k < 8; ++k) o[k] = glu_clamped_pair(v[2 * k], v[2 * k + 1], w, p.glu_limit, p.glu_alpha);
+            } else {
+#pragma unroll
+                for (int k = 0; k < 8; ++k) o[k] = swiglu_pair(v[2 * k], v[2 * k + 1]);
+            }
             if (col0 + 16 <= p.N && (((uintptr_t)dst) & 15) == 0) {
                 *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(o);
             } else {

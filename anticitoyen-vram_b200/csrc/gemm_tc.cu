@@ -223,7 +223,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     if (cluster_split) cluster_arrive();
     bool cluster_waited = false;
 
-    const int n_items = p.tiles_a * p.tiles_b * p.splits;
+    // a grouped product: how many tiles of A there are is known on the device only (the kernel that grouped the rows
+    // wrote it), so every thread waits for the kernels before this one and reads it; all roles then walk the same items
+    int tiles_a_now = p.tiles_a;
+    if (p.tile_expert) {
+        pdl_wait();
+        tiles_a_now = min(tiles_a_now, *p.tiles_used);
+    }
+    const int n_items = tiles_a_now * p.tiles_b * p.splits;
     const uint32_t tiles_addr = gt_smem(tiles);
 
     if (warp == 0) {
@@ -235,7 +242,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             if (p.early_w && (int)blockIdx.x < n_items) {
                 const int split = blockIdx.x % p.splits, tile = blockIdx.x / p.splits;
                 int ta, tb;
-                gt_tile_of(tile, p.tiles_a, p.tiles_b, p.group_a, ta, tb);
+                gt_tile_of(tile, tiles_a_now, p.tiles_b, p.group_a, ta, tb);
                 const int kb0 = split * p.kb_per_split, kb1 = min(kb0 + p.kb_per_split, p.n_kb);
                 early = min(STAGES, kb1 - kb0);
                 for (int i = 0; i < early; ++i) {
@@ -252,7 +259,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             for (int item = blockIdx.x; item < n_items && !abort_s; item += gridDim.x) {
                 const int split = item % p.splits, tile = item / p.splits;
                 int ta, tb;
-                gt_tile_of(tile, p.tiles_a, p.tiles_b, p.group_a, ta, tb);
+                gt_tile_of(tile, tiles_a_now, p.tiles_b, p.group_a, ta, tb);
                 const int kb0 = split * p.kb_per_split, kb1 = min(kb0 + p.kb_per_split, p.n_kb);
                 for (int kb = kb0; kb < kb1; ++kb, s = (s + 1 == STAGES ? 0 : s + 1), ph ^= (s == 0)) {
                     const uint32_t a_dst = tiles_addr + s * S::STAGE_BYTES;
@@ -268,7 +275,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     if (kb == p.skip_kb) continue;          // test of the bounded waits: the bytes announced never come
                     [[maybe_unused]] const unsigned long long tp1 = ACV_TL_NOW();
                     if (!(half_done && p.swap)) tma_load_2d(a_dst, &map_a, full0 + 8 * s, kb * GT_BK, ta * GT_BM);
-                    if (!(half_done && !p.swap)) tma_load_2d(a_dst + GT_BM * GT_BK * 2, &map_b, full0 + 8 * s, kb * GT_BK, tb * BN);
+                    if (!(half_done && !p.swap))
+                        tma_load_2d(a_dst + GT_BM * GT_BK * 2, &map_b, full0 + 8 * s, kb * GT_BK,
+                                    tb * BN + (p.tile_expert ? p.tile_expert[ta] * p.RB : 0));
                     ACV_TL_ADD(TL_M_SUM_LOAD_ISSUE, tp1);
                 }
             }
@@ -322,7 +331,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             // where each token of the tile stands and goes, and its angles: read now, needed when the tile leaves
             const int tile = blockIdx.x / p.splits;
             int ta0, tb;
-            gt_tile_of(tile, p.tiles_a, p.tiles_b, p.group_a, ta0, tb);
+            gt_tile_of(tile, tiles_a_now, p.tiles_b, p.group_a, ta0, tb);
             int* pos_s = reinterpret_cast<int*>(aux);
             int* pg_s = pos_s + BN;
             float* cs_s = reinterpret_cast<float*>(pg_s + BN);
@@ -356,7 +365,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         for (int item = blockIdx.x; item < n_items && !abort_s; item += gridDim.x, ++local) {
             const int split = item % p.splits, tile = item / p.splits;
             int ta, tb;
-            gt_tile_of(tile, p.tiles_a, p.tiles_b, p.group_a, ta, tb);
+            gt_tile_of(tile, tiles_a_now, p.tiles_b, p.group_a, ta, tb);
             const uint32_t buf = local & 1, use = local >> 1;
             if (!mbar_wait(tfull0 + 8 * buf, use & 1, &abort_s, p.wait_limit)) { abort_s = 1; atomicExch(p.status, 4); break; }
             tc_fence_after();
@@ -477,7 +486,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             const int wq = warp & 3;
             const int tile = blockIdx.x / p.splits;
             int ta, tb;
-            gt_tile_of(tile, p.tiles_a, p.tiles_b, p.group_a, ta, tb);
+            gt_tile_of(tile, tiles_a_now, p.tiles_b, p.group_a, ta, tb);
             const int row_a = ta * GT_BM + wq * 32 + lane;
             const uint32_t taddr = tmem_base + ((uint32_t)(wq * 32) << 16);
             const float* part = reinterpret_cast<const float*>(tiles + STAGES * S::STAGE_BYTES + 256) + wq * 32 + lane;
@@ -804,6 +813,8 @@ static int gemm_tc_run(GemmParams& p, const void* x, int ldx, const void* w, int
     p.RB = swap ? M : N;
     p.K = K; p.M = M; p.N = N; p.ldc = ldc; p.swap = swap; p.out_f32 = out_f32; p.act = act; p.cluster = flags & 1; p.early_w = (flags >> 1) & 1;
     if (act && (out_f32 || (N & 1))) return ACV_ERR_SIZE;
+    if (act == 2 && swap) return ACV_ERR_SIZE;
+    if (p.tile_expert && (swap || splits > 1 || (flags & 6) || p.experts < 1 || (N % 8))) return ACV_ERR_SIZE;
     p.tiles_a = (p.RA + GT_BM - 1) / GT_BM;
     p.tiles_b = (p.RB + bn - 1) / bn;
     p.n_kb = (K + GT_BK - 1) / GT_BK;
@@ -829,7 +840,7 @@ static int gemm_tc_run(GemmParams& p, const void* x, int ldx, const void* w, int
         if (rc) return rc;
         return launch_gemm_pair(ma, mb, p, sm_count, stages, stream);
     }
-    rc = make_map(&mb, b_ptr, p.RB, K, swap ? ldx : ldw, bn);
+    rc = make_map(&mb, b_ptr, p.tile_expert ? p.RB * p.experts : p.RB, K, swap ? ldx : ldw, bn);
     if (rc) return rc;
     switch (bn) {
         case 16: return launch_gemm<16>(ma, mb, p, sm_count, stages, stream);
@@ -853,10 +864,27 @@ ACV_API int acv_gemm_tc(const void* x, int ldx, const void* w, int ldw, void* C,
                         int out_f32, int act, int swap, int bn, int splits, float* workspace, long long workspace_floats,
                         int* counters, long long n_counters, int* status, int sm_count, int stages, int flags,
                         cudaStream_t stream) {
-    GemmParams p;
+    GemmParams p = {};
     p.qkv = 0;
     return gemm_tc_run(p, x, ldx, w, ldw, C, ldc, M, N, K, out_f32, act, swap, bn, splits, workspace, workspace_floats,
                        counters, n_counters, status, sm_count, stages, flags, stream);
+}
+
+// Grouped product, tokens on rows: x [M, K] holds rows grouped by expert in tiles of 128 (tile_expert[i]: the expert of
+// rows [128 i, 128 i + 128); *tiles_used: how many tiles hold rows, both on the device); w stacks `experts` matrices of N
+// rows; C [M, N] (act 0: bfloat16 or float) or [M, N / 2] (act 2: (gate, up) pairs of rows through the clamped gated
+// unit, the accumulators times row_scale[row] first).  Tiles beyond *tiles_used are not computed.
+ACV_API int acv_gemm_tc_grouped(const void* x, int ldx, const void* w, int ldw, void* C, int ldc, int M, int N, int K,
+                                int experts, const int* tile_expert, const int* tiles_used, int out_f32, int act,
+                                const float* row_scale, float limit, float alpha, int bn, int* status, int sm_count,
+                                int stages, cudaStream_t stream) {
+    GemmParams p = {};
+    p.qkv = 0;
+    p.tile_expert = tile_expert; p.tiles_used = tiles_used; p.experts = experts;
+    p.row_scale = row_scale; p.glu_limit = limit; p.glu_alpha = alpha;
+    if (!tile_expert || !tiles_used || (M % GT_BM)) return ACV_ERR_SIZE;
+    return gemm_tc_run(p, x, ldx, w, ldw, C, ldc, M, N, K, out_f32, act, 0, bn, 1, nullptr, 0, nullptr, 0, status, sm_count,
+                       stages, 0, stream);
 }
 
 // The stacked q,k,v projection with its epilogue: C [M, (NH + 2 NKV) D] gets the normed and rotated queries (its
@@ -874,7 +902,7 @@ ACV_API int acv_gemm_tc_qkv(const void* x, int ldx, const void* w, int ldw, void
         !positions || !seq_of_token || !block_table || page_size <= 0 || ((uintptr_t)k_pages & 15) || ((uintptr_t)v_pages & 15) ||
         (cos_sin && ((uintptr_t)cos_sin & 15)))
         return ACV_ERR_SIZE;
-    GemmParams p;
+    GemmParams p = {};
     p.qkv = 1; p.q_heads = NH; p.kv_heads = NKV; p.head_dim = D; p.q_w = q_w; p.k_w = k_w; p.qk_eps = eps;
     p.cos_sin = cos_sin; p.table_rows = table_rows; p.positions = positions; p.seq_of_token = seq_of_token;
     p.block_table = block_table; p.bt_stride = bt_stride; p.bt_rows = bt_rows; p.k_pages = (bf16*)k_pages; p.v_pages = (bf16*)v_pages;

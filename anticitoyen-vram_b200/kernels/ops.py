@@ -84,11 +84,13 @@ def _declare(lib: ctypes.CDLL) -> None:
         "acv_heads_norm_append": [P, P, I, P, P, I, I, I, I, I, I, I, P, P, F, P, P, P, I, P, P, P, I, I, I, P],
         "acv_diff_combine": [P, I, P, I, I, I, I, F, F, F, I, P],
         "acv_diff_attention_generic": [P, I, P, I, P, P, P, P, P, I, P, I, I, I, I, I, I, I, F, I, I, F, F, F, I, P],
-        "acv_moe_route": [P, I, P, P, I, I, I, I, I, I, P, P, P, I, P],
-        "acv_moe_group": [P, I, I, I, P, P, P, P],
-        "acv_moe_gemm_simt": [P, I, P, LL, I, P, I, P, P, P, I, I, I, I, I, F, F, I, P],
-        "acv_moe_gemm_mma": [P, I, P, LL, I, P, I, P, P, P, I, I, I, I, I, F, F, P],
-        "acv_moe_combine": [P, I, P, I, P, I, P, P, I, I, I, I, P],
+        "acv_moe_route": [P, I, P, P, P, I, I, I, I, I, I, I, P, P, P, I, P],
+        "acv_moe_group": [P, I, I, I, I, P, P, P, P, P],
+        "acv_moe_gather": [P, I, P, P, I, I, P, P, P, I, I, P],
+        "acv_gemm_tc_grouped": [P, I, P, I, P, I, I, I, I, I, P, P, I, I, P, F, F, I, P, I, I, P],
+        "acv_moe_gemm_simt": [P, I, P, LL, I, P, I, P, P, P, I, I, I, I, I, F, F, I, I, P],
+        "acv_moe_gemm_mma": [P, I, P, LL, I, P, I, P, P, P, I, I, I, I, I, F, F, I, P],
+        "acv_moe_combine": [P, I, I, P, I, P, I, P, P, I, I, I, I, P],
         "acv_glu": [P, I, P, I, I, I, I, F, F, I, P],
         "acv_argmax": [P, I, I, I, P, P],
         "acv_apply_penalties": [P, I, I, P, P, P, I, P, P, P, P],
@@ -1017,34 +1019,88 @@ MOE_TILE = 64               # rows of a tile of the grouped products (MOE_TILE o
 GLU_SWISH_CLAMPED = 0       # g = min(a, limit), u = clamp(b, +-limit): g * sigmoid(alpha g) * (u + 1)
 
 
-def moe_max_tiles(rows: int, experts: int) -> int:
+MOE_TC_TILE = 128           # rows of a tile of the grouped tcgen05 product (GT_BM of csrc/gemm_epilogue.cuh)
+MOE_TC_ROWS = 1024          # from this many (token, choice) rows on, aligned bfloat16 steps group for the tcgen05 product
+
+
+def moe_max_tiles(rows: int, experts: int, tile: int = MOE_TILE) -> int:
     """Tiles that ``rows`` (token, choice) rows can need at most, whatever the routing: every expert may leave one
     tile partly filled."""
-    return -(-rows // MOE_TILE) + experts
+    return -(-rows // tile) + experts
 
 
-def moe_route(h: torch.Tensor, w_router: torch.Tensor, gate_w: torch.Tensor | None, top: int, softmax: bool, renorm: bool,
-              ids: torch.Tensor, weights: torch.Tensor, gate: torch.Tensor | None) -> None:
-    """Router of a mixture of experts, in 32-bit: ids, weights [T, top] (int32, float32); gate [T] = sigmoid(h . gate_w)."""
-    _need_cuda(h, w_router, ids, weights)
+def moe_route(h: torch.Tensor, w_router: torch.Tensor | None, gate_w: torch.Tensor | None, top: int, softmax: bool, renorm: bool,
+              ids: torch.Tensor, weights: torch.Tensor, gate: torch.Tensor | None, logits: torch.Tensor | None = None,
+              experts: int | None = None) -> None:
+    """Router of a mixture of experts, in 32-bit: ids, weights [T, top] (int32, float32); gate [T] = sigmoid(h . gate_w).
+    With ``logits`` (float32 [T, >= experts (+ 1)]: the router's columns, then the gate's) the products were made before
+    and only the scores and the choice are made here."""
+    _need_cuda(h, ids, weights)
+    T, H = h.shape
+    if logits is not None:
+        if logits.dtype != torch.float32 or logits.stride(1) != 1 or experts is None:
+            raise KernelError("moe_route: float32 logits and the number of experts are wanted")
+        _check(library().acv_moe_route(None, 0, None, None, _p(logits), logits.stride(0), T, H, experts, top, int(softmax),
+                                       int(renorm), _p(ids), _p(weights), _p(gate), dtype_code(h.dtype), _stream()), "moe_route")
+        return
     if w_router.dtype != torch.float32 or not w_router.is_contiguous() or h.stride(1) != 1:
         raise KernelError("moe_route: a contiguous float32 router matrix is wanted")
-    T, H = h.shape
-    _check(library().acv_moe_route(_p(h), h.stride(0), _p(w_router), _p(gate_w), T, H, w_router.shape[0], top, int(softmax),
-                                   int(renorm), _p(ids), _p(weights), _p(gate), dtype_code(h.dtype), _stream()), "moe_route")
+    _check(library().acv_moe_route(_p(h), h.stride(0), _p(w_router), _p(gate_w), None, 0, T, H, w_router.shape[0], top,
+                                   int(softmax), int(renorm), _p(ids), _p(weights), _p(gate), dtype_code(h.dtype), _stream()),
+           "moe_route")
 
 
-def moe_group(ids: torch.Tensor, experts: int, grouped: torch.Tensor, place: torch.Tensor, tile_expert: torch.Tensor) -> None:
-    """Group the rows (token, choice) by expert: ``grouped`` [tiles * MOE_TILE] holds the rows expert after expert, each
-    expert's padded with -1 to whole tiles; ``place`` [rows] where a row went; ``tile_expert`` [tiles] whose a tile is."""
+def moe_group(ids: torch.Tensor, experts: int, grouped: torch.Tensor, place: torch.Tensor, tile_expert: torch.Tensor,
+              tile: int = MOE_TILE, tiles_used: torch.Tensor | None = None) -> None:
+    """Group the rows (token, choice) by expert: ``grouped`` [tiles * tile] holds the rows expert after expert, each
+    expert's padded with -1 to whole tiles; ``place`` [rows] where a row went; ``tile_expert`` [tiles] whose a tile is;
+    ``tiles_used`` (one int32, optional): how many tiles hold rows."""
     _need_cuda(ids, grouped, place, tile_expert)
-    _check(library().acv_moe_group(_p(ids), ids.numel(), experts, tile_expert.numel(), _p(grouped), _p(place),
-                                   _p(tile_expert), _stream()), "moe_group")
+    if grouped.numel() < tile_expert.numel() * tile:
+        raise KernelError("moe_group: the grouped list is shorter than its tiles")
+    _check(library().acv_moe_group(_p(ids), ids.numel(), experts, tile_expert.numel(), tile, _p(grouped), _p(place),
+                                   _p(tile_expert), _p(tiles_used), _stream()), "moe_group")
+
+
+def moe_gather(h: torch.Tensor, grouped: torch.Tensor, weights: torch.Tensor | None, top: int, out: torch.Tensor,
+               scale_out: torch.Tensor | None, tiles_used: torch.Tensor | None, tile: int) -> torch.Tensor:
+    """out[r] = h[grouped[r] // top] (zeros where grouped[r] < 0), scale_out[r] = weights[grouped[r]]: the tokens' rows in
+    grouped order (bfloat16, rows of 16-byte alignment); rows behind the tiles in use are left as they are."""
+    _need_cuda(h, grouped, out)
+    if h.dtype != torch.bfloat16 or out.dtype != torch.bfloat16 or not out.is_contiguous() or h.stride(1) != 1:
+        raise KernelError("moe_gather: bfloat16 rows are wanted")
+    _check(library().acv_moe_gather(_p(h), h.stride(0), _p(grouped), _p(weights), top, h.shape[1], _p(out), _p(scale_out),
+                                    _p(tiles_used), tile, out.shape[0], _stream()), "moe_gather")
+    return out
+
+
+def gemm_tc_grouped(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, tile_expert: torch.Tensor, tiles_used: torch.Tensor,
+                    glu: bool = False, row_scale: torch.Tensor | None = None, limit: float = 0.0, alpha: float = 0.0) -> torch.Tensor:
+    """The experts' products on tcgen05: x [tiles * 128, K] holds the rows in grouped order, w [E, N, K] the experts'
+    matrices; out [rows, N] (bfloat16 or float32), or with ``glu`` [rows, N / 2] bfloat16: w's rows come in (gate, up) pairs
+    and go through the clamped gated unit, the accumulators times ``row_scale[row]`` first."""
+    _need_cuda(x, w, out, tile_expert, tiles_used)
+    E, N, K = w.shape
+    M = x.shape[0]
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or not w.is_contiguous() or x.shape[1] != K or x.stride(1) != 1 \
+            or out.shape != (M, N // 2 if glu else N) or out.stride(1) != 1 or M != tile_expert.numel() * MOE_TC_TILE:
+        raise KernelError(f"gemm_tc_grouped: shapes {tuple(x.shape)} x {tuple(w.shape)} -> {tuple(out.shape)} do not fit")
+    if glu and out.dtype != torch.bfloat16:
+        raise KernelError("gemm_tc_grouped: the gated output is bfloat16")
+    bn = 256 if N >= 256 else (128 if N >= 128 else 64)
+    _, _, status = _gemm_buffers(x.device, 0, 0)
+    _check(library().acv_gemm_tc_grouped(_p(x), x.stride(0), _p(w), K, _p(out), out.stride(0), M, N, K, E, _p(tile_expert),
+                                         _p(tiles_used), 1 if out.dtype == torch.float32 else 0, 2 if glu else 0,
+                                         _p(row_scale), limit, alpha, bn, _p(status), sm_count(x.device), 8, _stream()),
+           "gemm_tc_grouped")
+    return out
 
 
 def moe_gemm_simt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, grouped: torch.Tensor, tile_expert: torch.Tensor,
-                  row_weight: torch.Tensor | None, top: int, glu: bool, limit: float = 0.0, alpha: float = 0.0) -> torch.Tensor:
-    """The experts' products over the grouped rows on the CUDA cores, 32-bit accumulation.
+                  row_weight: torch.Tensor | None, top: int, glu: bool, limit: float = 0.0, alpha: float = 0.0,
+                  pairs: bool = False) -> torch.Tensor:
+    """The experts' products over the grouped rows on the CUDA cores, 32-bit accumulation.  ``pairs``: with ``glu``, the
+    rows of w are (gate, up) pairs instead of all gate rows followed by all up rows.
 
     ``glu``: w [E, 2N, K] (gate rows, then up rows), a [T, K] the tokens, out [tiles * MOE_TILE, N] of a's type =
     act(weight * gate, weight * up).  Otherwise w [E, N, K], a the grouped rows [tiles * MOE_TILE, K], out float32
@@ -1057,7 +1113,7 @@ def moe_gemm_simt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, grouped: 
         raise KernelError(f"moe_gemm_simt: shapes {tuple(a.shape)} x {tuple(w.shape)} -> {tuple(out.shape)} do not fit")
     _check(library().acv_moe_gemm_simt(_p(a), a.stride(0), _p(w), w.stride(0), w.stride(1), _p(out), out.stride(0),
                                        _p(grouped), _p(tile_expert), _p(row_weight), top, tile_expert.numel(), N, K,
-                                       0 if glu else 1, limit, alpha, dtype_code(a.dtype), _stream()), "moe_gemm_simt")
+                                       0 if glu else 1, limit, alpha, int(pairs), dtype_code(a.dtype), _stream()), "moe_gemm_simt")
     return out
 
 
@@ -1069,7 +1125,8 @@ def moe_gemm_mma_takes(a: torch.Tensor, w: torch.Tensor) -> bool:
 
 
 def moe_gemm_mma(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, grouped: torch.Tensor, tile_expert: torch.Tensor,
-                 row_weight: torch.Tensor | None, top: int, glu: bool, limit: float = 0.0, alpha: float = 0.0) -> torch.Tensor:
+                 row_weight: torch.Tensor | None, top: int, glu: bool, limit: float = 0.0, alpha: float = 0.0,
+                 pairs: bool = False) -> torch.Tensor:
     """``moe_gemm_simt`` on the tensor cores (bfloat16 operands, float accumulators; the same arguments)."""
     _need_cuda(a, w, out, grouped, tile_expert)
     E, NW, K = w.shape
@@ -1078,16 +1135,16 @@ def moe_gemm_mma(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, grouped: t
         raise KernelError(f"moe_gemm_mma: shapes {tuple(a.shape)} x {tuple(w.shape)} -> {tuple(out.shape)} do not fit")
     _check(library().acv_moe_gemm_mma(_p(a), a.stride(0), _p(w), w.stride(0), w.stride(1), _p(out), out.stride(0),
                                       _p(grouped), _p(tile_expert), _p(row_weight), top, tile_expert.numel(), N, K,
-                                      0 if glu else 1, limit, alpha, _stream()), "moe_gemm_mma")
+                                      0 if glu else 1, limit, alpha, int(pairs), _stream()), "moe_gemm_mma")
     return out
 
 
 def moe_experts_up(h: torch.Tensor, gate_up: torch.Tensor, act: torch.Tensor, grouped: torch.Tensor, tile_expert: torch.Tensor,
-                   row_weight: torch.Tensor | None, top: int, limit: float, alpha: float) -> torch.Tensor:
+                   row_weight: torch.Tensor | None, top: int, limit: float, alpha: float, pairs: bool = False) -> torch.Tensor:
     """act[grouped row] = gated activation of the row's expert's gate and up products of its token; dispatch by shape."""
     if moe_gemm_mma_takes(h, gate_up):
-        return moe_gemm_mma(h, gate_up, act, grouped, tile_expert, row_weight, top, True, limit, alpha)
-    return moe_gemm_simt(h, gate_up, act, grouped, tile_expert, row_weight, top, True, limit, alpha)
+        return moe_gemm_mma(h, gate_up, act, grouped, tile_expert, row_weight, top, True, limit, alpha, pairs)
+    return moe_gemm_simt(h, gate_up, act, grouped, tile_expert, row_weight, top, True, limit, alpha, pairs)
 
 
 def moe_experts_down(act: torch.Tensor, down: torch.Tensor, out: torch.Tensor, grouped: torch.Tensor, tile_expert: torch.Tensor,
@@ -1100,10 +1157,11 @@ def moe_experts_down(act: torch.Tensor, down: torch.Tensor, out: torch.Tensor, g
 
 def moe_combine(d: torch.Tensor, place: torch.Tensor, top: int, shared: torch.Tensor | None, gate: torch.Tensor | None,
                 out: torch.Tensor) -> torch.Tensor:
-    """out[t] = sum_j d[place[t, j]] (+ gate[t] * shared[t]), summed in float32 in the order of the choices."""
+    """out[t] = sum_j d[place[t, j]] (+ gate[t] * shared[t]), summed in float32 in the order of the choices
+    (d float32, or bfloat16 beside a bfloat16 output)."""
     _need_cuda(d, place, out)
     T, H = out.shape
-    _check(library().acv_moe_combine(_p(d), d.stride(0), _p(place), top, _p(shared), shared.stride(0) if shared is not None else 0,
+    _check(library().acv_moe_combine(_p(d), d.stride(0), dtype_code(d.dtype), _p(place), top, _p(shared), shared.stride(0) if shared is not None else 0,
                                      _p(gate), _p(out), out.stride(0), T, H, dtype_code(out.dtype), _stream()), "moe_combine")
     return out
 

@@ -115,7 +115,7 @@ class DecoderModel:
         cache_bytes, flops = 0, self.head.flops(logit_rows)
         for e in self.plan.schedule:
             block = self.blocks[e.layer]
-            weight_bytes += block.weight_bytes()
+            weight_bytes += block.step_weight_bytes(T) if hasattr(block, "step_weight_bytes") else block.weight_bytes()
             flops += block.flops(T)
             mixer = getattr(block, "mixer", None)
             if mixer is not None and e.cache >= 0:

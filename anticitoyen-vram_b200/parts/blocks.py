@@ -59,6 +59,13 @@ class PreNormBlock:
     def weight_bytes(self) -> int:
         return sum(p.weight_bytes() for p in (self.input_norm, self.post_norm, self.mixer, self.feed_forward) if p is not None)
 
+    def step_weight_bytes(self, num_tokens: int) -> int:
+        """Weights that a step of ``num_tokens`` tokens reads: a part that reads only some of its weights (routed
+        experts) says how many (``step_weight_bytes``); every other part reads all of them."""
+        parts = (self.input_norm, self.post_norm, self.mixer, self.feed_forward)
+        return sum(p.step_weight_bytes(num_tokens) if hasattr(p, "step_weight_bytes") else p.weight_bytes()
+                   for p in parts if p is not None)
+
     def flops(self, num_tokens: int) -> float:
         return self.mixer.flops(num_tokens) + (self.feed_forward.flops(num_tokens) if self.feed_forward is not None else 0.0)
 

@@ -122,14 +122,29 @@ class RoutedExperts(FeedForward):
         p = self.prefix
         w = lambda n: tensors[p + n].to(device=rt.device, dtype=rt.dtype)
         self.router = tensors[p + "router"].to(device=rt.device, dtype=torch.float32).contiguous()
-        # [E, 2F, H]: an expert's gate rows, then its up rows; [E, H, F]
-        self.gate_up = torch.stack([torch.cat([w(f"e{e}.gate"), w(f"e{e}.up")], dim=0) for e in range(self.experts)]).contiguous()
+        self.run_dtype = rt.dtype
+        # [E, 2F, H]: an expert's gate and up rows; [E, H, F].  bfloat16 with rows of 16-byte alignment: (gate, up) row by
+        # row, the layout that the tcgen05 product's epilogue wants (the other kernels read either); else all gate
+        # rows, then all up rows
+        self.pairs = rt.dtype == torch.bfloat16 and self.hidden_size % 8 == 0 and self.expert_ff % 8 == 0
+        self.gate_up = torch.stack([
+            torch.stack([w(f"e{e}.gate"), w(f"e{e}.up")], dim=1).reshape(2 * self.expert_ff, self.hidden_size) if self.pairs
+            else torch.cat([w(f"e{e}.gate"), w(f"e{e}.up")], dim=0) for e in range(self.experts)]).contiguous()
         self.down = torch.stack([w(f"e{e}.down") for e in range(self.experts)]).contiguous()
         self.shared_gate_up = self.shared_down = self.shared_gate = None
         if self.shared_ff:
             self.shared_gate_up = Linear.stacked([w("shared.gate"), w("shared.up")])
             self.shared_down = Linear(w("shared.down"))
             self.shared_gate = tensors[p + "shared.sg"].to(device=rt.device, dtype=torch.float32).reshape(-1).contiguous()
+        # The router's logits (and the shared gate's) as one matrix product with 32-bit accumulation: in a float32 run
+        # the CUDA-core product; in a bfloat16 run the tensor-core product with float output, which is the same 32-bit
+        # arithmetic when the weights are bfloat16 values anyway (products of two bfloat16 numbers are exact in float).
+        # Weights that bfloat16 cannot hold keep the router kernel that reads them as float.
+        rows = [self.router] + ([self.shared_gate[None, :]] if self.shared_ff else [])
+        stacked = torch.cat(rows + [torch.zeros((-len(torch.cat(rows)) % 8, self.hidden_size), device=rt.device)])
+        self.router_linear = None
+        if rt.dtype == torch.float32 or bool((stacked.to(torch.bfloat16).float() == stacked).all()):
+            self.router_linear = Linear(stacked.to(rt.dtype))
 
     # ---- cost of a step
     def weight_bytes(self) -> int:
@@ -140,11 +155,12 @@ class RoutedExperts(FeedForward):
             n += self.shared_gate_up.weight_bytes() + self.shared_down.weight_bytes() + self.shared_gate.numel() * 4
         return n
 
-    def active_weight_bytes(self, num_tokens: int) -> int:
-        """Weights that a step of ``num_tokens`` tokens reads at most: no more experts than rows."""
-        active = min(self.experts, num_tokens * self.top)
+    def step_weight_bytes(self, num_tokens: int) -> int:
+        """Weights that a step of ``num_tokens`` tokens is expected to read: the experts that at least one token
+        chooses when choices fall evenly, E (1 - (1 - top/E)^tokens), and everything that runs for every token."""
+        active = self.experts * (1.0 - (1.0 - self.top / self.experts) ** num_tokens)
         per = (self.gate_up.numel() + self.down.numel()) // self.experts * self.gate_up.element_size()
-        n = self.router.numel() * 4 + active * per
+        n = self.router.numel() * 4 + int(active * per)
         if self.shared_ff:
             n += self.shared_gate_up.weight_bytes() + self.shared_down.weight_bytes() + self.shared_gate.numel() * 4
         return n
@@ -163,16 +179,42 @@ class RoutedExperts(FeedForward):
         ids = torch.empty(rows, device=dev, dtype=torch.int32)
         weights = torch.empty(rows, device=dev, dtype=torch.float32)
         gate = torch.empty(T, device=dev, dtype=torch.float32) if self.shared_ff else None
-        ops.moe_route(h, self.router, self.shared_gate, top, self.scoring == "softmax", self.renormalize, ids, weights, gate)
-        grouped = torch.empty(tiles * ops.MOE_TILE, device=dev, dtype=torch.int32)
+        if self.router_linear is not None:
+            # many tokens against a few dozen router rows: one column of tiles, so the reduction is split eight ways
+            # to put more than a ninth of the SMs to work
+            plan = (0, 128, 8, 4, 0) if h.dtype == torch.bfloat16 and T >= 512 and H >= 2048 and self.router_linear.out_features <= 128 else None
+            logits = self.router_linear(h, out_dtype=torch.float32, plan=plan)
+            ops.moe_route(h, None, None, top, self.scoring == "softmax", self.renormalize, ids, weights, gate, logits=logits,
+                          experts=E)
+        else:
+            ops.moe_route(h, self.router, self.shared_gate, top, self.scoring == "softmax", self.renormalize, ids, weights, gate)
         place = torch.empty(rows, device=dev, dtype=torch.int32)
-        tile_expert = torch.empty(tiles, device=dev, dtype=torch.int32)
-        ops.moe_group(ids, E, grouped, place, tile_expert)
-        act = torch.empty((tiles * ops.MOE_TILE, F), device=dev, dtype=h.dtype)
-        ops.moe_experts_up(h, self.gate_up, act, grouped, tile_expert, weights if self.weight_on == "input" else None, top,
-                           self.expert_limit, self.alpha)
-        parts = torch.empty((tiles * ops.MOE_TILE, H), device=dev, dtype=torch.float32)
-        ops.moe_experts_down(act, self.down, parts, grouped, tile_expert, weights if self.weight_on == "output" else None, top)
+        w_in = weights if self.weight_on == "input" else None
+        w_out = weights if self.weight_on == "output" else None
+        if self.pairs and rows >= ops.MOE_TC_ROWS and w_out is None:
+            # many rows: tiles of 128 rows on the tcgen05 product, the tokens' rows copied into grouped order first
+            tile = ops.MOE_TC_TILE
+            tiles = ops.moe_max_tiles(rows, E, tile)
+            grouped = torch.empty(tiles * tile, device=dev, dtype=torch.int32)
+            tile_expert = torch.empty(tiles, device=dev, dtype=torch.int32)
+            used = torch.empty(1, device=dev, dtype=torch.int32)
+            ops.moe_group(ids, E, grouped, place, tile_expert, tile, used)
+            hg = torch.empty((tiles * tile, H), device=dev, dtype=h.dtype)
+            scale = torch.empty(tiles * tile, device=dev, dtype=torch.float32)
+            ops.moe_gather(h, grouped, w_in, top, hg, scale, used, tile)
+            act = torch.empty((tiles * tile, F), device=dev, dtype=h.dtype)
+            ops.gemm_tc_grouped(hg, self.gate_up, act, tile_expert, used, True, scale, self.expert_limit, self.alpha)
+            # the experts' outputs leave the product as bfloat16 (as every projection's do); their sum is 32-bit
+            parts = torch.empty((tiles * tile, H), device=dev, dtype=h.dtype)
+            ops.gemm_tc_grouped(act, self.down, parts, tile_expert, used)
+        else:
+            grouped = torch.empty(tiles * ops.MOE_TILE, device=dev, dtype=torch.int32)
+            tile_expert = torch.empty(tiles, device=dev, dtype=torch.int32)
+            ops.moe_group(ids, E, grouped, place, tile_expert)
+            act = torch.empty((tiles * ops.MOE_TILE, F), device=dev, dtype=h.dtype)
+            ops.moe_experts_up(h, self.gate_up, act, grouped, tile_expert, w_in, top, self.expert_limit, self.alpha, self.pairs)
+            parts = torch.empty((tiles * ops.MOE_TILE, H), device=dev, dtype=torch.float32)
+            ops.moe_experts_down(act, self.down, parts, grouped, tile_expert, w_out, top)
         shared = None
         if self.shared_ff:
             gu = self.shared_gate_up(h)

@@ -52,7 +52,9 @@ class Linear:
     def flops(self, tokens: int) -> float:
         return 2.0 * tokens * self.out_features * self.in_features
 
-    def __call__(self, x: torch.Tensor, out_dtype: torch.dtype | None = None) -> torch.Tensor:
+    def __call__(self, x: torch.Tensor, out_dtype: torch.dtype | None = None, plan: tuple | None = None) -> torch.Tensor:
+        """``plan``: how the tensor-core product tiles and splits this call (``ops.gemm_tc``), for a caller that knows
+        its shape better than the general rules do."""
         w = self.weight
         out_dtype = out_dtype or x.dtype
         out = torch.empty((x.shape[0], self.out_features), device=x.device, dtype=out_dtype)
@@ -60,6 +62,8 @@ class Linear:
             return out
         if x.dtype == torch.float32:
             ops.gemm_simt(x, w, out)
+        elif out_dtype == torch.float32 and plan is not None and ops.gemm_tc_takes(x, w):
+            ops.gemm_tc(x, w, out, plan=plan, static_weights=True)
         elif out_dtype == torch.float32:
             ops.linear_bf16_f32out(x, w, out, static_weights=True)
         else:

@@ -295,6 +295,92 @@ def run_ours(args) -> int:
     return 0
 
 
+# ---------------------------------------------------------------------- another design beside its closest relative
+ZOTONEX_SIZES = {
+    # width, heads, kv heads, dim (a head has two query vectors of it), vdim, chunk, experts, top, expert ff, shared ff
+    "s": dict(width=2048, heads=16, kv_heads=4, dim=64, vdim=128, chunk=1024, experts=32, top=4, ff=512, shared_ff=1024),
+    "m": dict(width=4096, heads=32, kv_heads=8, dim=64, vdim=128, chunk=2048, experts=64, top=6, ff=768, shared_ff=1536),
+}
+
+
+def run_design(args) -> int:
+    """``--design zotonex``: prefill and decode throughput of the Zotonex design at layer sizes of real models (random
+    weights, a few layers), beside a Qwen3 model of equal size: the same width, as many heads of the same value size,
+    and an intermediate size equal to what a Zotonex token's experts add up to (top * ff + shared ff).  Whole steps
+    through the step function, and one layer's mixer and feed-forward alone with their rooflines (L2 flushed before
+    each timed run).  One JSON line."""
+    import torch
+
+    from acvram_b200 import bench as B
+    from acvram_b200.config import Qwen3Config, ZotonexConfig
+    from acvram_b200.engine.runner import ModelRunner
+    from acvram_b200.models import build_random
+
+    pk, pk_src = peaks()
+    K, W = args.steps, args.warmup
+    page = 64
+    layers, vocab = args.layers or 4, 32768
+    out = {"design": "zotonex", "beside": "qwen3", "layers": layers, "vocab": vocab, "dtype": "bf16", "page_size": page,
+           "data": "synthetic token ids, random weights", "peaks": {**pk, "source": pk_src}, "sizes": {}}
+    for name in args.sizes.split(","):
+        z = ZOTONEX_SIZES[name]
+        layer = {"type": "attention",
+                 "mixer": {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["vdim"], "diff": 0.5,
+                           "scale": z["dim"] ** -0.5, "mask": {"size": z["chunk"]}},
+                 "mlp": {"kind": "moe", "router": {"experts": z["experts"], "top": z["top"]}, "expert": {"ff": z["ff"], "limit": 7.0},
+                         "shared": {"ff": z["shared_ff"], "limit": 7.0}}}
+        zcfg = ZotonexConfig.from_dict({"architecture": "Zotonex", "vocab": vocab, "width": z["width"], "norm": {"eps": 1e-5},
+                                        "embedding": {"scale": 1.0}, "logit_scale": 1.0, "layers": [layer] * layers})
+        qcfg = Qwen3Config(vocab_size=vocab, hidden_size=z["width"], intermediate_size=z["top"] * z["ff"] + z["shared_ff"],
+                           num_hidden_layers=layers, num_attention_heads=z["heads"], num_key_value_heads=z["kv_heads"],
+                           head_dim=z["vdim"], rms_norm_eps=1e-6, rope_theta=1e6, max_position_embeddings=8192,
+                           tie_word_embeddings=False)
+        res = {"zotonex": dict(z), "qwen3": {"hidden": qcfg.hidden_size, "intermediate": qcfg.intermediate_size,
+                                            "q_heads": qcfg.num_attention_heads, "kv_heads": qcfg.num_key_value_heads,
+                                            "head_dim": qcfg.head_dim}}
+        for arm, cfg in (("zotonex", zcfg), ("qwen3", qcfg)):
+            model = build_random(cfg, seed=0, dtype=torch.bfloat16, device="cuda:0")
+            batch_max = 64
+            tokens = batch_max * (args.context + 2 * (K + W) + 2 * page) + 4096
+            runner = ModelRunner(model, page, tokens // page + 8, batch_max + 2, max_len=8192)
+            if not args.no_cuda_graphs:
+                runner.enable_graphs()
+            r = {"weights_gb": round(model.weight_bytes() / 1e9, 3)}
+            try:
+                pre = B.time_prefill(runner, 2048, reps=5, warmup=3)
+                flops = B.prefill_flops(model, 2048)
+                r["prefill_2048"] = {"tokens_per_s": round(pre["tokens_per_s"], 1), "ms": round(pre["ms"], 3),
+                                     "tflops_frac": round(flops / (pre["ms"] * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}
+                for b in (8, 64):
+                    names = [f"d{b}-{i}" for i in range(b)]
+                    B.fill_contexts(runner, names, args.context)
+                    try:
+                        d = B.time_decode(runner, names, K, W)
+                    finally:
+                        for n in names:
+                            runner.release(n)
+                    nbytes = B.decode_step_bytes(model, b, args.context + W + K // 2)
+                    r[f"decode_b{b}"] = {"tokens_per_s": round(d["tokens_per_s"], 1), "ms_per_step": round(d["ms_per_step"], 4),
+                                         "hbm_frac": round(nbytes / (d["ms_per_step"] * 1e-3) / 1e9 / pk["hbm_gbs"], 4)}
+                # one layer's parts alone: a prompt of 2048 tokens (bound by the tensor cores) and 64 requests that
+                # decode at 2048-token contexts (bound by memory)
+                for label, ql, kl in (("prefill_2048", [2048], [2048]), ("decode_b64", [1] * 64, [args.context] * 64)):
+                    parts = B.time_parts(runner, ql, kl)
+                    for part, v in parts.items():
+                        sec = v["ms"] * 1e-3
+                        r[f"{part}_{label}"] = {"us": round(v["ms"] * 1e3, 1),
+                                                "tflops_frac": round(v["flops"] / sec / (pk["bf16_tflops"] * 1e12), 4),
+                                                "hbm_frac": round(v["bytes"] / sec / 1e9 / pk["hbm_gbs"], 4)}
+            except B.Refused as exc:
+                r["refused"] = str(exc)
+            res[arm + "_result"] = r
+            del runner, model
+            _free_device_memory()
+        out["sizes"][name] = res
+    print(json.dumps(out))
+    return 0
+
+
 def bench_config(args, cfg, layers: int, full_layers: int, page: int, graphs: bool) -> dict:
     """The configuration's sizes, flat, the same keys in both arms (the reference arm fills what it knows)."""
     return {"model": f"Qwen3-{args.shape.upper()} shape", "layers": layers, "layers_full": full_layers, "hidden": cfg["hidden_size"],
@@ -318,6 +404,9 @@ def main() -> int:
     ap.add_argument("--page-size", type=int, default=16, help="tokens in a page of the cache (the engine's own default is 64)")
     ap.add_argument("--skip-points", action="store_true", help="skip the batch 1 and 64 points")
     ap.add_argument("--no-cuda-graphs", action="store_true")
+    ap.add_argument("--design", default="", choices=["", "zotonex"],
+                    help="measure another design beside its closest relative instead of the headline (see run_design)")
+    ap.add_argument("--sizes", default="s,m", help="with --design: which of its sizes (s: width 2048, m: width 4096)")
     ap.add_argument("--time-limit", type=float, default=240.0,
                     help="seconds after which the points at the 14B and 32B layer sizes are left out (and named as left out)")
     args = ap.parse_args()
@@ -328,6 +417,8 @@ def main() -> int:
         args.warmup = 3
     if args.impl == "reference":
         return run_reference(args)
+    if args.design:
+        return run_design(args)
     return run_ours(args)
 
 

@@ -189,7 +189,8 @@ def moe_case(T, H, E, top, F, S, seed, dtype):
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["float32", "bfloat16"])
 @pytest.mark.parametrize("shape", [(1, 64, 3, 1, 48, 0), (5, 100, 5, 3, 36, 20), (300, 128, 8, 2, 64, 128), (77, 96, 6, 6, 40, 56),
-                                   (130, 256, 16, 4, 192, 0)], ids=lambda s: "t%d-h%d-e%d-top%d-f%d-s%d" % s)
+                                   (130, 256, 16, 4, 192, 0), (700, 128, 8, 2, 64, 128), (520, 256, 16, 4, 192, 0),
+                                   (1100, 64, 3, 1, 40, 24), (600, 2048, 8, 2, 64, 72)], ids=lambda s: "t%d-h%d-e%d-top%d-f%d-s%d" % s)
 def test_routed_experts_part(shape, dtype):
     from acvram_b200.parts import PartSpec, Runtime, build
     T, H, E, top, F, S = shape
@@ -203,6 +204,7 @@ def test_routed_experts_part(shape, dtype):
         f["shared"] = {"ff": S, "limit": 0.75}
     want = pz.mixture(h.double(), {k: v.double() for k, v in w.items()}, f)
     err = zu.row_errors(got, want)
+    # (from 1024 (token, choice) rows on, the bfloat16 run goes through the grouped tcgen05 product)
     # bfloat16: products are rounded to bfloat16 on their way (activations, the shared expert's output)
     assert float(err.max()) < (1e-4 if dtype == torch.float32 else 0.02), (float(err.max()), int(err.argmax()))
 
