@@ -214,7 +214,54 @@ def decode_layer_case(batch: int, context: int, reps: int, fused: bool) -> dict:
     return {"kernel": "decode_layer" if fused else "separate", "batch": batch, "context": context, "us_per_layer": us}
 
 
+def moe_case(tokens: int, reps: int, H: int = 4096, E: int = 64, top: int = 6, F: int = 768) -> dict:
+    """The experts' two grouped products of a mixture (64 experts of 768 at width 4096, six a token) for a step of
+    ``tokens`` tokens with choices drawn evenly: the tcgen05 form from 1024 rows on, the mma.sync form below.  The
+    weights (1.2 GB) are larger than the L2; what is reported is the useful work, 6 * rows * F * H operations, and the
+    weights of the experts that were chosen."""
+    dev = "cuda"
+    gate_up = torch.randn(E, 2 * F, H, device=dev, dtype=torch.bfloat16) * 0.02
+    down = torch.randn(E, H, F, device=dev, dtype=torch.bfloat16) * 0.02
+    h = torch.randn(tokens, H, device=dev, dtype=torch.bfloat16)
+    rows = tokens * top
+    ids = torch.stack([torch.randperm(E, device=dev)[:top] for _ in range(tokens)]).to(torch.int32).reshape(-1)
+    weights = torch.rand(rows, device=dev)
+    place = torch.empty(rows, device=dev, dtype=torch.int32)
+    big = rows >= ops.MOE_TC_ROWS
+    tile = ops.MOE_TC_TILE if big else ops.MOE_TILE
+    tiles = ops.moe_max_tiles(rows, E, tile)
+    grouped = torch.empty(tiles * tile, device=dev, dtype=torch.int32)
+    tile_expert = torch.empty(tiles, device=dev, dtype=torch.int32)
+    used = torch.empty(1, device=dev, dtype=torch.int32)
+    ops.moe_group(ids, E, grouped, place, tile_expert, tile, used)
+    act = torch.empty(tiles * tile, F, device=dev, dtype=torch.bfloat16)
+    if big:
+        hg = torch.empty(tiles * tile, H, device=dev, dtype=torch.bfloat16)
+        scale = torch.empty(tiles * tile, device=dev)
+        ops.moe_gather(h, grouped, weights, top, hg, scale, used, tile)
+        parts = torch.empty(tiles * tile, H, device=dev, dtype=torch.bfloat16)
+        up = lambda i: ops.gemm_tc_grouped(hg, gate_up, act, tile_expert, used, True, scale, 7.0, 1.702)
+        dn = lambda i: ops.gemm_tc_grouped(act, down, parts, tile_expert, used)
+    else:
+        parts = torch.empty(tiles * tile, H, device=dev, dtype=torch.float32)
+        up = lambda i: ops.moe_gemm_mma(h, gate_up, act, grouped, tile_expert, weights, top, True, 7.0, 1.702, True)
+        dn = lambda i: ops.moe_gemm_mma(act, down, parts, grouped, tile_expert, None, top, False)
+    us_up, us_dn = _time(up, reps), _time(dn, reps)
+    chosen = int(torch.unique(ids).numel())
+    form = "tcgen05" if big else "mma.sync"
+    print(f"moe experts ({form}) tokens={tokens} rows={rows} experts chosen={chosen}/{E}: gate/up {us_up:.1f} us "
+          f"({4.0 * rows * F * H / us_up / 1e6:.0f} TFLOP/s, {chosen * 2 * F * H * 2 / us_up / 1e3:.0f} GB/s of weights), "
+          f"down {us_dn:.1f} us ({2.0 * rows * F * H / us_dn / 1e6:.0f} TFLOP/s, {chosen * F * H * 2 / us_dn / 1e3:.0f} GB/s)")
+    return {"kernel": f"moe_{form}", "tokens": tokens, "rows": rows, "experts_chosen": chosen, "us_gate_up": us_up,
+            "us_down": us_dn, "tflops_gate_up": 4.0 * rows * F * H / us_up / 1e6, "tflops_down": 2.0 * rows * F * H / us_dn / 1e6,
+            "weights_gbs_gate_up": chosen * 2 * F * H * 2 / us_up / 1e3, "weights_gbs_down": chosen * F * H * 2 / us_dn / 1e3}
+
+
 CASES = {
+    "moe_decode_b64": lambda r: moe_case(64, r),
+    "moe_decode_b8": lambda r: moe_case(8, r),
+    "moe_prefill": lambda r: moe_case(2048, r),
+    "moe_prefill_8k": lambda r: moe_case(8192, r),
     "gemm_decode": lambda r: gemm_case(8, 6144, 4096, r),
     "gemm_decode_mlp": lambda r: gemm_case(8, 24576, 4096, r),
     "gemm_decode_b64": lambda r: gemm_case(64, 24576, 4096, r),
