@@ -148,7 +148,6 @@ __global__ void moe_group_kernel(const int* __restrict__ ids, int N, int E, int 
     pdl_launch_dependents();
     pdl_wait();
     for (int e = threadIdx.x; e < E; e += blockDim.x) count[e] = 0;
-    for (int i = threadIdx.x; i < max_tiles * tile_rows; i += blockDim.x) grouped[i] = -1;
     for (int i = threadIdx.x; i < max_tiles; i += blockDim.x) tile_expert[i] = -1;
     __syncthreads();
     for (int r = threadIdx.x; r < N; r += blockDim.x) {
@@ -166,9 +165,13 @@ __global__ void moe_group_kernel(const int* __restrict__ ids, int N, int E, int 
         if (tiles_used) *tiles_used = at / tile_rows;
     }
     __syncthreads();
+    // the places behind an expert's rows, up to the end of its last tile, hold no row (tiles that belong to no expert
+    // are never read)
     for (int e = threadIdx.x; e < E; e += blockDim.x) {
         for (int i = start[e] / tile_rows; i < start[e + 1] / tile_rows; ++i)
             if (i < max_tiles) tile_expert[i] = e;
+        for (int i = start[e] + count[e]; i < start[e + 1]; ++i)
+            if (i < max_tiles * tile_rows) grouped[i] = -1;
         count[e] = 0;       // now the cursor inside the expert's rows
     }
     __syncthreads();

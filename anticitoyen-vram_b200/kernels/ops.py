@@ -1020,7 +1020,8 @@ GLU_SWISH_CLAMPED = 0       # g = min(a, limit), u = clamp(b, +-limit): g * sigm
 
 
 MOE_TC_TILE = 128           # rows of a tile of the grouped tcgen05 product (GT_BM of csrc/gemm_epilogue.cuh)
-MOE_TC_ROWS = 1024          # from this many (token, choice) rows on, aligned bfloat16 steps group for the tcgen05 product
+MOE_TC_ROWS = 1024          # from this many (token, choice) rows on, aligned bfloat16 steps group for the tcgen05 product,
+MOE_TC_ROWS_PER_EXPERT = 32  # if an expert gets this many on average (tiles of 128 rows would else be nearly empty)
 
 
 def moe_max_tiles(rows: int, experts: int, tile: int = MOE_TILE) -> int:

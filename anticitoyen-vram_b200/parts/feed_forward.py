@@ -191,7 +191,7 @@ class RoutedExperts(FeedForward):
         place = torch.empty(rows, device=dev, dtype=torch.int32)
         w_in = weights if self.weight_on == "input" else None
         w_out = weights if self.weight_on == "output" else None
-        if self.pairs and rows >= ops.MOE_TC_ROWS and w_out is None:
+        if self.pairs and rows >= ops.MOE_TC_ROWS and rows >= ops.MOE_TC_ROWS_PER_EXPERT * E and w_out is None:
             # many rows: tiles of 128 rows on the tcgen05 product, the tokens' rows copied into grouped order first
             tile = ops.MOE_TC_TILE
             tiles = ops.moe_max_tiles(rows, E, tile)

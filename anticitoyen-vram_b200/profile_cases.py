@@ -227,7 +227,7 @@ def moe_case(tokens: int, reps: int, H: int = 4096, E: int = 64, top: int = 6, F
     ids = torch.stack([torch.randperm(E, device=dev)[:top] for _ in range(tokens)]).to(torch.int32).reshape(-1)
     weights = torch.rand(rows, device=dev)
     place = torch.empty(rows, device=dev, dtype=torch.int32)
-    big = rows >= ops.MOE_TC_ROWS
+    big = rows >= ops.MOE_TC_ROWS and rows >= ops.MOE_TC_ROWS_PER_EXPERT * E
     tile = ops.MOE_TC_TILE if big else ops.MOE_TILE
     tiles = ops.moe_max_tiles(rows, E, tile)
     grouped = torch.empty(tiles * tile, device=dev, dtype=torch.int32)
