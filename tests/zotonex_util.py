@@ -51,8 +51,8 @@ def config(which: str) -> dict:
                   {"type": "attention", "mixer": mixer(3, 3, 24, 40, None, kv_from=0), "mlp": None}]
         return _model(157, 100, layers, 1e-5, 10.0, 0.25)
     if which == "D":
-        layers = [{"type": "attention", "mixer": mixer(4, 2, 32, 64, 48), "mlp": moe(4, 2, 64, 2.0, 128, 1.5)},
-                  {"type": "attention", "mixer": mixer(4, 1, 64, 128, 48), "mlp": moe(4, 2, 64, 2.0, 128, 1.5)},
+        layers = [{"type": "attention", "mixer": mixer(4, 2, 32, 64, 48), "mlp": moe(4, 2, 72, 2.25, 136, 1.25)},
+                  {"type": "attention", "mixer": mixer(4, 1, 64, 128, 48), "mlp": moe(4, 2, 72, 2.25, 136, 1.25)},
                   {"type": "attention", "mixer": mixer(4, 1, 64, 128, 80, kv_from=1), "mlp": None}]
         return _model(320, 128, layers, 1e-5, 11.3, 0.5)
     raise KeyError(which)
