@@ -870,6 +870,17 @@ ACV_API int acv_gemm_tc(const void* x, int ldx, const void* w, int ldw, void* C,
                        counters, n_counters, status, sm_count, stages, flags, stream);
 }
 
+// The product with the clamped gated unit as its epilogue (tokens on rows only): w's rows are (gate, up) pairs,
+// C [M, N / 2] bfloat16 = g * sigmoid(alpha g) * (u + 1), g = min(gate, limit), u = clamp(up, +-limit).
+ACV_API int acv_gemm_tc_glu(const void* x, int ldx, const void* w, int ldw, void* C, int ldc, int M, int N, int K, float limit,
+                            float alpha, int bn, int* status, int sm_count, int stages, int flags, cudaStream_t stream) {
+    GemmParams p = {};
+    p.qkv = 0;
+    p.glu_limit = limit; p.glu_alpha = alpha;
+    return gemm_tc_run(p, x, ldx, w, ldw, C, ldc, M, N, K, 0, 2, 0, bn, 1, nullptr, 0, nullptr, 0, status, sm_count, stages,
+                       flags & ~1, stream);
+}
+
 // Grouped product, tokens on rows: x [M, K] holds rows grouped by expert in tiles of 128 (tile_expert[i]: the expert of
 // rows [128 i, 128 i + 128); *tiles_used: how many tiles hold rows, both on the device); w stacks `experts` matrices of N
 // rows; C [M, N] (act 0: bfloat16 or float) or [M, N / 2] (act 2: (gate, up) pairs of rows through the clamped gated

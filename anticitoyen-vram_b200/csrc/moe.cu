@@ -554,29 +554,31 @@ ACV_API int acv_moe_combine(const void* D, int ldd, int d_dtype, const int* plac
 }
 
 // ----------------------------------------------------------------------------- gated activation of a stacked product
-// gu [T, 2I]: gate columns, then up columns (one expert applied to every token, e.g. a shared expert).
+// gu [T, 2I]: gate columns, then up columns, or with `pairs` (gate, up) column by column (one expert applied to every
+// token, e.g. a shared expert).
 template <typename T>
 __global__ void glu_kernel(const T* __restrict__ gu, int ldg, T* __restrict__ out, int ldo, int I, size_t total, float limit,
-                           float alpha) {
+                           float alpha, int pairs) {
     pdl_launch_dependents();
     pdl_wait();
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
         const size_t t = idx / I;
         const int i = (int)(idx - t * I);
-        out[t * ldo + i] = from_f32<T>(glu_act<T>(to_f32(gu[t * ldg + i]), to_f32(gu[t * ldg + I + i]), limit, alpha));
+        const float a = to_f32(gu[t * ldg + (pairs ? 2 * i : i)]), b = to_f32(gu[t * ldg + (pairs ? 2 * i + 1 : I + i)]);
+        out[t * ldo + i] = from_f32<T>(glu_act<T>(a, b, limit, alpha));
     }
 }
 
 ACV_API int acv_glu(const void* gu, int ldg, void* out, int ldo, int T_tokens, int I, int kind, float limit, float alpha,
-                    int dtype, cudaStream_t stream) {
+                    int pairs, int dtype, cudaStream_t stream) {
     const size_t total = (size_t)T_tokens * I;
     if (total == 0) return 0;
     if (kind != GLU_SWISH_CLAMPED) return ACV_ERR_SIZE;
     const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
     if (dtype == ACV_F32)
-        acv_launch(PDL_ACT, glu_kernel<float>, blocks, 256, 0, stream, (const float*)gu, ldg, (float*)out, ldo, I, total, limit, alpha);
+        acv_launch(PDL_ACT, glu_kernel<float>, blocks, 256, 0, stream, (const float*)gu, ldg, (float*)out, ldo, I, total, limit, alpha, pairs);
     else if (dtype == ACV_BF16)
-        acv_launch(PDL_ACT, glu_kernel<bf16>, blocks, 256, 0, stream, (const bf16*)gu, ldg, (bf16*)out, ldo, I, total, limit, alpha);
+        acv_launch(PDL_ACT, glu_kernel<bf16>, blocks, 256, 0, stream, (const bf16*)gu, ldg, (bf16*)out, ldo, I, total, limit, alpha, pairs);
     else
         return ACV_ERR_DTYPE;
     return acv_launch_status();

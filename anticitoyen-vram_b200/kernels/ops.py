@@ -91,7 +91,8 @@ def _declare(lib: ctypes.CDLL) -> None:
         "acv_moe_gemm_simt": [P, I, P, LL, I, P, I, P, P, P, I, I, I, I, I, F, F, I, I, P],
         "acv_moe_gemm_mma": [P, I, P, LL, I, P, I, P, P, P, I, I, I, I, I, F, F, I, P],
         "acv_moe_combine": [P, I, I, P, I, P, I, P, P, I, I, I, I, P],
-        "acv_glu": [P, I, P, I, I, I, I, F, F, I, P],
+        "acv_glu": [P, I, P, I, I, I, I, F, F, I, I, P],
+        "acv_gemm_tc_glu": [P, I, P, I, P, I, I, I, I, F, F, I, P, I, I, I, P],
         "acv_argmax": [P, I, I, I, P, P],
         "acv_apply_penalties": [P, I, I, P, P, P, I, P, P, P, P],
         "acv_sample": [P, I, I, I, P, P, P, P, P, P, P, P, P],
@@ -1167,10 +1168,36 @@ def moe_combine(d: torch.Tensor, place: torch.Tensor, top: int, shared: torch.Te
     return out
 
 
-def glu(gate_up: torch.Tensor, out: torch.Tensor, kind: int, limit: float, alpha: float) -> torch.Tensor:
-    """out = act(gate_up[:, :I], gate_up[:, I:]) for a gated unit's stacked product [T, 2I]."""
+def glu(gate_up: torch.Tensor, out: torch.Tensor, kind: int, limit: float, alpha: float, pairs: bool = False) -> torch.Tensor:
+    """out = act(gate, up) for a gated unit's stacked product [T, 2I]: gate columns then up columns, or with ``pairs``
+    (gate, up) column by column."""
     _need_cuda(gate_up, out)
     T, I = out.shape
-    _check(library().acv_glu(_p(gate_up), gate_up.stride(0), _p(out), out.stride(0), T, I, kind, limit, alpha,
+    _check(library().acv_glu(_p(gate_up), gate_up.stride(0), _p(out), out.stride(0), T, I, kind, limit, alpha, int(pairs),
                              dtype_code(out.dtype), _stream()), "glu")
+    return out
+
+
+def linear_bf16_glu_takes(x: torch.Tensor, w_pairs: torch.Tensor) -> bool:
+    """The product with the clamped gated unit in its epilogue exists with tokens on the tensor core's rows: more than
+    128 tokens, rows of 16-byte alignment."""
+    return x.dtype == torch.bfloat16 and x.shape[0] > 128 and gemm_tc_takes(x, w_pairs) and w_pairs.shape[0] % 16 == 0
+
+
+def linear_bf16_glu(x: torch.Tensor, w_pairs: torch.Tensor, out: torch.Tensor, limit: float, alpha: float) -> torch.Tensor:
+    """out[M, I] = g * sigmoid(alpha g) * (u + 1), g = min(x . w[2i], limit), u = clamp(x . w[2i + 1], +-limit), in one
+    kernel (the activation is the tcgen05 product's epilogue)."""
+    _need_cuda(x, w_pairs, out)
+    M, K = x.shape
+    N = w_pairs.shape[0]
+    if out.shape != (M, N // 2) or out.dtype != torch.bfloat16 or out.stride(1) != 1 or w_pairs.shape[1] != K:
+        raise KernelError(f"linear_bf16_glu: shapes {tuple(x.shape)} x {tuple(w_pairs.shape)} -> {tuple(out.shape)} do not fit")
+    plan = gemm_tc_plan(M, N, K)
+    if plan[0]:
+        raise KernelError("linear_bf16_glu: tokens must lie on the rows (more than 128 of them)")
+    bn, stages = plan[1], plan[3] if len(plan) > 3 else 8
+    mode = plan[4] if len(plan) > 4 else 0
+    _, _, status = _gemm_buffers(x.device, 0, 0)
+    _check(library().acv_gemm_tc_glu(_p(x), x.stride(0), _p(w_pairs), w_pairs.stride(0), _p(out), out.stride(0), M, N, K, limit,
+                                     alpha, bn, _p(status), sm_count(x.device), stages, mode | 2, _stream()), "gemm_tc_glu")
     return out

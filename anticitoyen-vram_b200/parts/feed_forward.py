@@ -133,7 +133,11 @@ class RoutedExperts(FeedForward):
         self.down = torch.stack([w(f"e{e}.down") for e in range(self.experts)]).contiguous()
         self.shared_gate_up = self.shared_down = self.shared_gate = None
         if self.shared_ff:
-            self.shared_gate_up = Linear.stacked([w("shared.gate"), w("shared.up")])
+            # with rows of 16-byte alignment in bfloat16: (gate, up) row by row, so that a step of many tokens applies the
+            # activation in the product's epilogue
+            self.shared_pairs = rt.dtype == torch.bfloat16 and self.hidden_size % 8 == 0 and self.shared_ff % 8 == 0
+            self.shared_gate_up = (Linear(torch.stack([w("shared.gate"), w("shared.up")], dim=1).reshape(2 * self.shared_ff, self.hidden_size))
+                                   if self.shared_pairs else Linear.stacked([w("shared.gate"), w("shared.up")]))
             self.shared_down = Linear(w("shared.down"))
             self.shared_gate = tensors[p + "shared.sg"].to(device=rt.device, dtype=torch.float32).reshape(-1).contiguous()
         # The router's logits (and the shared gate's) as one matrix product with 32-bit accumulation: in a float32 run
@@ -217,9 +221,12 @@ class RoutedExperts(FeedForward):
             ops.moe_experts_down(act, self.down, parts, grouped, tile_expert, w_out, top)
         shared = None
         if self.shared_ff:
-            gu = self.shared_gate_up(h)
             sact = torch.empty((T, self.shared_ff), device=dev, dtype=h.dtype)
-            ops.glu(gu, sact, ops.GLU_SWISH_CLAMPED, self.shared_limit, self.alpha)
+            if self.shared_pairs and ops.linear_bf16_glu_takes(h, self.shared_gate_up.weight):
+                ops.linear_bf16_glu(h, self.shared_gate_up.weight, sact, self.shared_limit, self.alpha)
+            else:
+                gu = self.shared_gate_up(h)
+                ops.glu(gu, sact, ops.GLU_SWISH_CLAMPED, self.shared_limit, self.alpha, self.shared_pairs)
             shared = self.shared_down(sact)
         out = torch.empty((T, H), device=dev, dtype=h.dtype)
         return ops.moe_combine(parts, place, top, shared, gate, out)
