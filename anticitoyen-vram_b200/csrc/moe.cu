@@ -139,6 +139,7 @@ ACV_API int acv_moe_route(const void* h, int h_stride, const float* w_router, co
 // to the next multiple hold -1.  tile_expert[i] names the expert of tile i (-1: no such tile).
 // The order of an expert's rows among themselves is whatever the atomics make it; a row's result does
 // not depend on its place.
+#define GR_BATCH 8
 __global__ void moe_group_kernel(const int* __restrict__ ids, int N, int E, int max_tiles, int tile_rows,
                                  int* __restrict__ grouped, int* __restrict__ place, int* __restrict__ tile_expert,
                                  int* __restrict__ tiles_used) {
@@ -150,9 +151,18 @@ __global__ void moe_group_kernel(const int* __restrict__ ids, int N, int E, int 
     for (int e = threadIdx.x; e < E; e += blockDim.x) count[e] = 0;
     for (int i = threadIdx.x; i < max_tiles; i += blockDim.x) tile_expert[i] = -1;
     __syncthreads();
-    for (int r = threadIdx.x; r < N; r += blockDim.x) {
-        const int e = ids[r];
-        if (e >= 0 && e < E) atomicAdd(&count[e], 1);
+    // rows in batches of GR_BATCH per thread: the batch's loads are issued together, so that the loop waits for memory
+    // once a batch and not once a row (the block is alone on the device and nothing hides its latencies)
+    for (int r0 = threadIdx.x; r0 < N; r0 += blockDim.x * GR_BATCH) {
+        int e[GR_BATCH];
+#pragma unroll
+        for (int b = 0; b < GR_BATCH; ++b) {
+            const int r = r0 + b * blockDim.x;
+            e[b] = r < N ? ids[r] : -1;
+        }
+#pragma unroll
+        for (int b = 0; b < GR_BATCH; ++b)
+            if (e[b] >= 0 && e[b] < E) atomicAdd(&count[e[b]], 1);
     }
     __syncthreads();
     if (threadIdx.x == 0) {
@@ -175,12 +185,22 @@ __global__ void moe_group_kernel(const int* __restrict__ ids, int N, int E, int 
         count[e] = 0;       // now the cursor inside the expert's rows
     }
     __syncthreads();
-    for (int r = threadIdx.x; r < N; r += blockDim.x) {
-        const int e = ids[r];
-        if (e < 0 || e >= E) { place[r] = -1; continue; }
-        const int at = start[e] + atomicAdd(&count[e], 1);
-        place[r] = at;
-        grouped[at] = r;
+    for (int r0 = threadIdx.x; r0 < N; r0 += blockDim.x * GR_BATCH) {
+        int e[GR_BATCH];
+#pragma unroll
+        for (int b = 0; b < GR_BATCH; ++b) {
+            const int r = r0 + b * blockDim.x;
+            e[b] = r < N ? ids[r] : -2;
+        }
+#pragma unroll
+        for (int b = 0; b < GR_BATCH; ++b) {
+            const int r = r0 + b * blockDim.x;
+            if (e[b] == -2) continue;
+            if (e[b] < 0 || e[b] >= E) { place[r] = -1; continue; }
+            const int at = start[e[b]] + atomicAdd(&count[e[b]], 1);
+            place[r] = at;
+            grouped[at] = r;
+        }
     }
 }
 
@@ -332,13 +352,14 @@ ACV_API int acv_moe_gemm_simt(const void* A, int lda, const void* W, long long w
 // ----------------------------------------------------------------------------- grouped products on the tensor cores
 // bfloat16, mma.sync m16n8k16 with float accumulators.  A CTA of four warps owns a tile of MOE_TILE grouped rows x 64
 // output columns (with GLU: 64 gate and the 64 up columns of the same numbers); a warp owns 16 rows.  Operands come in
-// slabs of 64 k through two stages of 16-byte asynchronous copies into swizzled tiles: the rows of A gathered by the
+// slabs of 64 k through three stages of 16-byte asynchronous copies into swizzled tiles: the rows of A gathered by the
 // grouping (rows without a token are zero-filled), the expert's weight rows by the tile's expert.  Same epilogues as
 // the CUDA-core form: the row's weight times the accumulators, then the activation (GLU), or float output (down).
 // Rows of 16-byte alignment are needed: K, lda, ldw and the experts' stride multiples of 8.
 #define MM_BN 64
 #define MM_BK 64
 #define MM_THREADS 128
+#define MM_STAGES 3
 
 template <bool GLU>
 __global__ void __launch_bounds__(MM_THREADS)
@@ -402,14 +423,18 @@ moe_gemm_mma_kernel(const bf16* __restrict__ A, int lda, const bf16* __restrict_
         }
     const int nkb = (K + MM_BK - 1) / MM_BK;
     const int mi = lane >> 3, lr = lane & 7;
+    // three stages: while slab kb is multiplied, kb + 1 is landing and kb + 2 is asked for.  One barrier a slab: behind
+    // it slab kb has landed for every thread, and every warp is done with slab kb - 1, whose stage the next copies take.
     load(0, 0);
     cp_async_commit();
+    if (nkb > 1) load(1, 1);
+    cp_async_commit();
     for (int kb = 0; kb < nkb; ++kb) {
-        const int stage = kb & 1;
-        if (kb + 1 < nkb) load(kb + 1, stage ^ 1);
-        cp_async_commit();
+        const int stage = kb % MM_STAGES;
         cp_async_wait<1>();
         __syncthreads();
+        if (kb + 2 < nkb) load(kb + 2, (kb + 2) % MM_STAGES);
+        cp_async_commit();
         const uint32_t ab = smem_u32(mm_smem + stage * STAGE), wb = ab + A_BYTES;
         if (warp_has_rows)
 #pragma unroll
@@ -429,7 +454,6 @@ moe_gemm_mma_kernel(const bf16* __restrict__ A, int lda, const bf16* __restrict_
                 }
             }
         }
-        __syncthreads();
     }
 #pragma unroll
     for (int half = 0; half < 2; ++half) {
@@ -463,13 +487,13 @@ ACV_API int acv_moe_gemm_mma(const void* A, int lda, const void* W, long long w_
     if ((K % 8) || (lda % 8) || (ldw % 8) || (w_expert_stride % 8) || ((uintptr_t)A & 15) || ((uintptr_t)W & 15)) return ACV_ERR_ALIGN;
     dim3 grid((N + MM_BN - 1) / MM_BN, max_tiles);
     if (which == 0) {
-        const int smem = 2 * (MOE_TILE * MM_BK * 2 + 2 * MM_BN * MM_BK * 2);
+        const int smem = MM_STAGES * (MOE_TILE * MM_BK * 2 + 2 * MM_BN * MM_BK * 2);
         static AcvSmemConfig cfg;
         if (int rc = acv_ensure_smem(cfg, moe_gemm_mma_kernel<true>, smem)) return rc;
         acv_launch(PDL_GEMM, moe_gemm_mma_kernel<true>, grid, MM_THREADS, smem, stream, (const bf16*)A, lda, (const bf16*)W,
                    w_expert_stride, ldw, C, ldc, grouped, tile_expert, row_weight, top, N, K, limit, alpha, pairs);
     } else {
-        const int smem = 2 * (MOE_TILE * MM_BK * 2 + MM_BN * MM_BK * 2);
+        const int smem = MM_STAGES * (MOE_TILE * MM_BK * 2 + MM_BN * MM_BK * 2);
         static AcvSmemConfig cfg;
         if (int rc = acv_ensure_smem(cfg, moe_gemm_mma_kernel<false>, smem)) return rc;
         acv_launch(PDL_GEMM, moe_gemm_mma_kernel<false>, grid, MM_THREADS, smem, stream, (const bf16*)A, lda, (const bf16*)W,
