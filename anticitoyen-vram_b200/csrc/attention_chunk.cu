@@ -25,7 +25,7 @@ attn_chunk_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ o
                   const bf16* __restrict__ k_pages, const bf16* __restrict__ v_pages, const int* __restrict__ tile_seq,
                   const int* __restrict__ tile_q0, const int* __restrict__ cu_q, const int* __restrict__ kv_len,
                   const int* __restrict__ block_table, int bt_stride, const int* __restrict__ bt_rows, int NH, int NKV, int page_size, int page_shift,
-                  int pg_cap, int num_pages, float scale, int window, int chunk) {
+                  int pg_cap, int num_pages, float scale, int window, int chunk, int out_f32) {
     constexpr int CH = D / 8;
     constexpr int TILE_BYTES = AC_BN * D * 2;
     extern __shared__ __align__(128) unsigned char smem[];
@@ -241,6 +241,13 @@ attn_chunk_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ o
         const int r = r0 + hh * 8;
         if (r >= rows) continue;
         const float inv = l_run[hh] > 0.f ? 1.f / l_run[hh] : 0.f;
+        if (out_f32) {
+            float* of = reinterpret_cast<float*>(out) + (size_t)(tok0 + r) * out_stride + (size_t)h * D + (lane & 3) * 2;
+#pragma unroll
+            for (int i = 0; i < D / 8; ++i)
+                *reinterpret_cast<float2*>(of + i * 8) = make_float2(acc[i][2 * hh] * inv, acc[i][2 * hh + 1] * inv);
+            continue;
+        }
         bf16* o = out + (size_t)(tok0 + r) * out_stride + (size_t)h * D + (lane & 3) * 2;
 #pragma unroll
         for (int i = 0; i < D / 8; ++i) {
@@ -254,7 +261,7 @@ template <int D>
 static int launch_chunk(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,
                         const void* v_pages, const int* tile_seq, const int* tile_q0, int n_tiles, const int* cu_q,
                         const int* kv_len, const int* block_table, int bt_stride, const int* bt_rows, int NH, int NKV, int page_size,
-                        int num_pages, float scale, int window, int chunk, int max_kv, cudaStream_t stream) {
+                        int num_pages, float scale, int window, int chunk, int out_f32, int max_kv, cudaStream_t stream) {
     int page_shift = -1;
     for (int b = 0; b < 31; ++b)
         if ((1 << b) == page_size) page_shift = b;
@@ -266,7 +273,7 @@ static int launch_chunk(const void* q, int q_stride, void* out, int out_stride, 
     dim3 grid(n_tiles, NH);
     acv_launch(PDL_MISC, attn_chunk_kernel<D>, grid, AC_THREADS, smem, stream,
         (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)k_pages, (const bf16*)v_pages, tile_seq,
-        tile_q0, cu_q, kv_len, block_table, bt_stride, bt_rows, NH, NKV, page_size, page_shift, pg_cap, num_pages, scale, window, chunk);
+        tile_q0, cu_q, kv_len, block_table, bt_stride, bt_rows, NH, NKV, page_size, page_shift, pg_cap, num_pages, scale, window, chunk, out_f32);
     return acv_launch_status();
 }
 
@@ -275,7 +282,7 @@ static int launch_chunk(const void* q, int q_stride, void* out, int out_stride, 
 ACV_API int acv_attention_chunk(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,
                                 const void* v_pages, const int* tile_seq, const int* tile_q0, int n_tiles,
                                 const int* cu_q, const int* kv_len, const int* block_table, int bt_stride, const int* bt_rows, int NH,
-                                int NKV, int D, int page_size, int num_pages, float scale, int window, int chunk, int max_kv,
+                                int NKV, int D, int page_size, int num_pages, float scale, int window, int chunk, int out_f32, int max_kv,
                                 cudaStream_t stream) {
     if (n_tiles <= 0) return 0;
     if (NKV <= 0 || NH % NKV || NH > 65535) return ACV_ERR_SIZE;
@@ -283,7 +290,7 @@ ACV_API int acv_attention_chunk(const void* q, int q_stride, void* out, int out_
         ((uintptr_t)out & 3) || (out_stride & 1))
         return ACV_ERR_ALIGN;
 #define AC_ARGS q, q_stride, out, out_stride, k_pages, v_pages, tile_seq, tile_q0, n_tiles, cu_q, kv_len, block_table, \
-                bt_stride, bt_rows, NH, NKV, page_size, num_pages, scale, window, chunk, max_kv, stream
+                bt_stride, bt_rows, NH, NKV, page_size, num_pages, scale, window, chunk, out_f32, max_kv, stream
     switch (D) {
         case 64: return launch_chunk<64>(AC_ARGS);
         case 128: return launch_chunk<128>(AC_ARGS);

@@ -34,7 +34,9 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ 
                    const int* __restrict__ kv_len, const int* __restrict__ block_table, int bt_stride,
                    const int* __restrict__ bt_rows, int NH, int NKV, int page_size, int page_shift, int pg_cap, int num_pages, float scale, int window, int chunk_mask, int n_splits,
                    float* __restrict__ part_acc, float* __restrict__ part_ml, int* __restrict__ counters,
-                   int cluster_merge) {
+                   int flags) {
+    const int cluster_merge = flags & 1;        // the splits of a (request, kv-head) are one cluster
+    const bool out_f32 = flags & 2;             // out is float (a caller that goes on computing with the result in 32-bit)
     constexpr int CH = D / 8;                 // 16-byte chunks per row
     constexpr int AD_THREADS = NW * 32;
     constexpr int WT_BYTES = 16 * D * 2;                         // 16 keys (or values) of one kv-head
@@ -310,7 +312,11 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ 
             }
         }
         if (n_splits == 1) {
-            out[(size_t)tok * out_stride + (size_t)(kvh * n_rep + r) * D + d] = __float2bfloat16_rn(L > 0.f ? O / L : 0.f);
+            {
+                const size_t at = (size_t)tok * out_stride + (size_t)(kvh * n_rep + r) * D + d;
+                const float res = L > 0.f ? O / L : 0.f;
+                if (out_f32) reinterpret_cast<float*>(out)[at] = res; else out[at] = __float2bfloat16_rn(res);
+            }
         } else if (cluster_merge) {
             // the splits of a (request, kv-head) are the CTAs of one cluster: each puts its partial into rank 0's
             // shared memory, rank 0 merges them after the cluster barrier
@@ -354,7 +360,11 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ 
                     O += ps[d] * f;
                 }
             }
-            out[(size_t)tok * out_stride + (size_t)(kvh * n_rep + r) * D + d] = __float2bfloat16_rn(L > 0.f ? O / L : 0.f);
+            {
+                const size_t at = (size_t)tok * out_stride + (size_t)(kvh * n_rep + r) * D + d;
+                const float res = L > 0.f ? O / L : 0.f;
+                if (out_f32) reinterpret_cast<float*>(out)[at] = res; else out[at] = __float2bfloat16_rn(res);
+            }
         }
         return;
     }
@@ -405,7 +415,11 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ 
                 }
             }
         }
-        out[(size_t)tok * out_stride + (size_t)(kvh * n_rep + r) * D + d] = __float2bfloat16_rn(L > 0.f ? O / L : 0.f);
+        {
+                const size_t at = (size_t)tok * out_stride + (size_t)(kvh * n_rep + r) * D + d;
+                const float res = L > 0.f ? O / L : 0.f;
+                if (out_f32) reinterpret_cast<float*>(out)[at] = res; else out[at] = __float2bfloat16_rn(res);
+            }
     }
     if (tid == 0) counters[item * NKV + kvh] = 0;   // ready for the next launch
 }
@@ -509,7 +523,7 @@ static int launch_decode_with(const void* q, int q_stride, void* out, int out_st
                               cudaStream_t stream) {
     if (int rc = acv_ensure_smem(decode_smem_config<D, NW>(), attn_decode_kernel<D, NW>, smem)) return rc;
     dim3 grid(n_dec, NKV, n_splits);
-    acv_launch_cluster(PDL_ATTN, dim3(1, 1, cluster_merge ? n_splits : 1), attn_decode_kernel<D, NW>, grid, NW * 32, smem,
+    acv_launch_cluster(PDL_ATTN, dim3(1, 1, (cluster_merge & 1) ? n_splits : 1), attn_decode_kernel<D, NW>, grid, NW * 32, smem,
         stream, (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)k_pages, (const bf16*)v_pages, dec_tokens,
         dec_seqs, kv_len, block_table, bt_stride, bt_rows, NH, NKV, page_size, page_shift, pg_cap, num_pages, scale, window,
         chunk_mask, n_splits, part_acc, part_ml, counters, cluster_merge);
@@ -525,6 +539,8 @@ static int launch_decode(const void* q, int q_stride, void* out, int out_stride,
     int page_shift = -1;
     for (int b = 0; b < 31; ++b)
         if ((1 << b) == page_size) page_shift = b;
+    const int out_f32_bit = cluster_merge & 2;      // travels with the merge flag to the kernel
+    cluster_merge &= 1;
     if (n_splits < 2 || n_splits > 8) cluster_merge = 0;
     int pg_cap = 0, alone = 0;
     const int cluster = cluster_merge ? n_splits : 1;
@@ -532,7 +548,7 @@ static int launch_decode(const void* q, int q_stride, void* out, int out_stride,
     const int bound = chunk_mask > 0 && (window <= 0 || chunk_mask < window) ? chunk_mask : window;
 #define AD_LAUNCH_ARGS q, q_stride, out, out_stride, k_pages, v_pages, dec_tokens, dec_seqs, n_dec, kv_len, block_table, \
                        bt_stride, bt_rows, NH, NKV, page_size, page_shift, pg_cap, num_pages, scale, window, chunk_mask, n_splits, \
-                       part_acc, part_ml, counters, cluster_merge
+                       part_acc, part_ml, counters, cluster_merge | out_f32_bit
     if (decode_grid_has_sms<D>(cluster, (long long)n_dec * NKV * n_splits, &alone)) {
         int smem = decode_smem_bytes(D, NH / NKV, page_size, bound, n_splits, max_kv, cluster_merge, AD_WARPS_ALONE, &pg_cap);
         if (smem < alone) smem = alone;
@@ -558,13 +574,14 @@ ACV_API int acv_attention_decode(const void* q, int q_stride, void* out, int out
                                  const int* kv_len, const int* block_table, int bt_stride, const int* bt_rows, int NH,
                                  int NKV, int D, int page_size, int num_pages, float scale, int window, int chunk_mask, int n_splits, float* part_acc,
                                  float* part_ml, int* counters, long long scratch_floats, long long scratch_ml_floats,
-                                 long long scratch_counters, int max_kv, int cluster_merge, cudaStream_t stream) {
+                                 long long scratch_counters, int max_kv, int cluster_merge, int out_f32, cudaStream_t stream) {
     if (n_dec <= 0) return 0;
+    cluster_merge = (cluster_merge ? 1 : 0) | (out_f32 ? 2 : 0);
     if (NKV <= 0 || NH % NKV || NH / NKV > 16 || n_splits < 1 || n_splits > 65535 || NKV > 65535) return ACV_ERR_SIZE;
     if (((uintptr_t)q & 15) || ((size_t)q_stride * 2) % 16 || ((uintptr_t)k_pages & 15) || ((uintptr_t)v_pages & 15))
         return ACV_ERR_ALIGN;
     const long long n_rep = NH / NKV;
-    if (n_splits > 1 && !(cluster_merge && n_splits <= 8)) {
+    if (n_splits > 1 && !((cluster_merge & 1) && n_splits <= 8)) {
         const long long parts = (long long)n_dec * NKV * n_splits;
         if (parts * n_rep * D > scratch_floats || parts * n_rep * 2 > scratch_ml_floats ||
             (long long)n_dec * NKV > scratch_counters)
@@ -672,7 +689,7 @@ ACV_API int acv_attention_decode_static(const void* q, int q_stride, void* out, 
     if (e != cudaSuccess) return (int)e;
     return acv_attention_decode(q, q_stride, out, out_stride, k_pages, v_pages, dec_tokens, dec_seqs, n_dec, kv_len,
                                 block_table, bt_stride, nullptr, NH, NKV, D, page_size, num_pages, scale, window, 0, n_splits,
-                                part_acc, part_ml, cnt, acc_floats, ml_floats, counters, max_kv, 0, stream);
+                                part_acc, part_ml, cnt, acc_floats, ml_floats, counters, max_kv, 0, 0, stream);
 }
 
 ACV_TL_EXPORT(attention_decode)

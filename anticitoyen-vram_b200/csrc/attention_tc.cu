@@ -50,6 +50,7 @@ struct AttnTcParams {
     int bt_stride;
     const int* bt_rows;         // the row of block_table of each request of the batch (null: its index)
     int NH, NKV, page_size, page_shift, num_pages, window, chunk;
+    int out_f32;            // out is float [T, out_stride floats] instead of bfloat16
     float scale;
     int* status;
 };
@@ -336,7 +337,14 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
             for (int c0 = 0; c0 < D; c0 += 32) {
                 uint32_t o[32];
                 tc_ld32(tmem_o + c0, o);
-                if (r < rows) {
+                if (r < rows && p.out_f32) {
+                    float* dstf = reinterpret_cast<float*>(p.out) + (size_t)(tok0 + r) * p.out_stride + (size_t)(h0 + hs) * D;
+#pragma unroll
+                    for (int c = 0; c < 32; c += 4)
+                        *reinterpret_cast<float4*>(dstf + c0 + c) =
+                            make_float4(__uint_as_float(o[c]) * inv, __uint_as_float(o[c + 1]) * inv,
+                                        __uint_as_float(o[c + 2]) * inv, __uint_as_float(o[c + 3]) * inv);
+                } else if (r < rows) {
 #pragma unroll
                     for (int c = 0; c < 32; c += 8) {
                         uint4 pk;
@@ -379,7 +387,7 @@ static int launch_attn_tc(const CUtensorMap& mq, const CUtensorMap& mk, const CU
 ACV_API int acv_attention_tc(const void* q, int q_stride, int T, void* out, int out_stride, const void* k_pages,
                              const void* v_pages, const int* tile_seq, const int* tile_q0, int n_tiles, const int* cu_q,
                              const int* kv_len, const int* block_table, int bt_stride, const int* bt_rows, int NH, int NKV,
-                             int D, int page_size, int num_pages, float scale, int window, int chunk, int* status,
+                             int D, int page_size, int num_pages, float scale, int window, int chunk, int out_f32, int* status,
                              cudaStream_t stream) {
     if (n_tiles <= 0) return 0;
     if (NKV <= 0 || NH % NKV || NH > 65535 || (D != 64 && D != 128)) return ACV_ERR_SIZE;
@@ -403,7 +411,7 @@ ACV_API int acv_attention_tc(const void* q, int q_stride, int T, void* out, int 
     AttnTcParams p;
     p.out = (bf16*)out; p.out_stride = out_stride; p.tile_seq = tile_seq; p.tile_q0 = tile_q0; p.cu_q = cu_q;
     p.kv_len = kv_len; p.block_table = block_table; p.bt_stride = bt_stride; p.bt_rows = bt_rows; p.NH = NH; p.NKV = NKV;
-    p.page_size = page_size; p.page_shift = page_shift; p.num_pages = num_pages; p.window = window; p.chunk = chunk; p.scale = scale;
+    p.page_size = page_size; p.page_shift = page_shift; p.num_pages = num_pages; p.window = window; p.chunk = chunk; p.out_f32 = out_f32; p.scale = scale;
     p.status = status;
     if (D == 64) return launch_attn_tc<64>(mq, mk, mv, p, n_tiles, stream);
     return launch_attn_tc<128>(mq, mk, mv, p, n_tiles, stream);

@@ -260,8 +260,8 @@ ACV_API int acv_diff_attention_generic(const void* q, int q_stride, void* out, i
 // ----------------------------------------------------------------------------- the maps' outputs combined
 // maps: [T, NH * 2 rows of DV] (head h's map 1, then its map 2, as attention kernels with one query vector per head
 // leave them); out[t, h] = unit_rms(o1 - lambda o2) * out_scale, in 32-bit.  One warp per (token, head).
-template <typename T, int NR>
-__global__ void diff_combine_kernel(const T* __restrict__ maps, int maps_stride, T* __restrict__ out, int out_stride, int NH,
+template <typename T, typename TM, int NR>
+__global__ void diff_combine_kernel(const TM* __restrict__ maps, int maps_stride, T* __restrict__ out, int out_stride, int NH,
                                     int DV, float lambda, float eps, float out_scale) {
     pdl_launch_dependents();
     pdl_wait();
@@ -269,8 +269,8 @@ __global__ void diff_combine_kernel(const T* __restrict__ maps, int maps_stride,
     const int h = blockIdx.y * DA_WARPS + warp;
     const int t = blockIdx.x;
     if (h >= NH) return;
-    const T* a1 = maps + (size_t)t * maps_stride + (size_t)(2 * h) * DV;
-    const T* a2 = a1 + DV;
+    const TM* a1 = maps + (size_t)t * maps_stride + (size_t)(2 * h) * DV;
+    const TM* a2 = a1 + DV;
     float o[NR];
     float ss = 0.f;
 #pragma unroll
@@ -289,24 +289,31 @@ __global__ void diff_combine_kernel(const T* __restrict__ maps, int maps_stride,
     }
 }
 
-ACV_API int acv_diff_combine(const void* maps, int maps_stride, void* out, int out_stride, int T_tokens, int NH, int DV,
-                             float lambda, float eps, float out_scale, int dtype, cudaStream_t stream) {
+// maps_f32: the maps are float beside a bfloat16 output (they were never rounded: the difference of two nearly equal
+// maps keeps its digits)
+ACV_API int acv_diff_combine(const void* maps, int maps_stride, int maps_f32, void* out, int out_stride, int T_tokens, int NH,
+                             int DV, float lambda, float eps, float out_scale, int dtype, cudaStream_t stream) {
     if (T_tokens <= 0) return 0;
     if (DV <= 0 || DV > 256 || NH <= 0) return ACV_ERR_SIZE;
     dim3 grid(T_tokens, (NH + DA_WARPS - 1) / DA_WARPS);
     const int nr = (DV + 31) / 32;
-#define DC_CASE(TT, N)                                                                                                  \
+#define DC_CASE(TT, TM, N)                                                                                              \
     case N:                                                                                                             \
-        acv_launch(PDL_ATTN, diff_combine_kernel<TT, N>, grid, DA_WARPS * 32, 0, stream, (const TT*)maps, maps_stride,  \
-                   (TT*)out, out_stride, NH, DV, lambda, eps, out_scale);                                               \
+        acv_launch(PDL_ATTN, diff_combine_kernel<TT, TM, N>, grid, DA_WARPS * 32, 0, stream, (const TM*)maps,           \
+                   maps_stride, (TT*)out, out_stride, NH, DV, lambda, eps, out_scale);                                  \
         break;
+#define DC_ALL(TT, TM) switch (nr) { DC_CASE(TT, TM, 1) DC_CASE(TT, TM, 2) DC_CASE(TT, TM, 3) DC_CASE(TT, TM, 4) \
+                                     DC_CASE(TT, TM, 5) DC_CASE(TT, TM, 6) DC_CASE(TT, TM, 7) DC_CASE(TT, TM, 8) }
     if (dtype == ACV_F32) {
-        switch (nr) { DC_CASE(float, 1) DC_CASE(float, 2) DC_CASE(float, 3) DC_CASE(float, 4) DC_CASE(float, 5) DC_CASE(float, 6) DC_CASE(float, 7) DC_CASE(float, 8) }
+        DC_ALL(float, float)
+    } else if (dtype == ACV_BF16 && maps_f32) {
+        DC_ALL(bf16, float)
     } else if (dtype == ACV_BF16) {
-        switch (nr) { DC_CASE(bf16, 1) DC_CASE(bf16, 2) DC_CASE(bf16, 3) DC_CASE(bf16, 4) DC_CASE(bf16, 5) DC_CASE(bf16, 6) DC_CASE(bf16, 7) DC_CASE(bf16, 8) }
+        DC_ALL(bf16, bf16)
     } else {
         return ACV_ERR_DTYPE;
     }
+#undef DC_ALL
 #undef DC_CASE
     return acv_launch_status();
 }

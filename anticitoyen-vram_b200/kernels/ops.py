@@ -74,15 +74,15 @@ def _declare(lib: ctypes.CDLL) -> None:
         "acv_gemm_simt": [P, I, P, I, P, I, I, I, I, I, I, P],
         "acv_gemm_tc_qkv": [P, I, P, I, P, I, I, I, I, I, I, I, P, LL, P, LL, P, I, I, I, I, I, I, P, P, F, P, I, P, P, P, I, P, P, P, I, I, P],
         "acv_gemm_tc": [P, I, P, I, P, I, I, I, I, I, I, I, I, I, P, LL, P, LL, P, I, I, I, P],
-        "acv_attention_decode": [P, I, P, I, P, P, P, P, I, P, P, I, P, I, I, I, I, I, F, I, I, I, P, P, P, LL, LL, LL, I, I, P],
-        "acv_attention_tc": [P, I, I, P, I, P, P, P, P, I, P, P, P, I, P, I, I, I, I, I, F, I, I, P, P],
-        "acv_attention_chunk": [P, I, P, I, P, P, P, P, I, P, P, P, I, P, I, I, I, I, I, F, I, I, I, P],
+        "acv_attention_decode": [P, I, P, I, P, P, P, P, I, P, P, I, P, I, I, I, I, I, F, I, I, I, P, P, P, LL, LL, LL, I, I, I, P],
+        "acv_attention_tc": [P, I, I, P, I, P, P, P, P, I, P, P, P, I, P, I, I, I, I, I, F, I, I, I, P, P],
+        "acv_attention_chunk": [P, I, P, I, P, P, P, P, I, P, P, P, I, P, I, I, I, I, I, F, I, I, I, I, P],
         "acv_table_update": [P, I, I, P, I, P],
         "acv_embed_scaled": [P, P, P, I, I, I, F, I, P],
         "acv_add_rmsnorm_f32": [P, P, P, P, P, I, I, F, I, P],
         "acv_scale_f32": [P, LL, F, P],
         "acv_heads_norm_append": [P, P, I, P, P, I, I, I, I, I, I, I, P, P, F, P, P, P, I, P, P, P, I, I, I, P],
-        "acv_diff_combine": [P, I, P, I, I, I, I, F, F, F, I, P],
+        "acv_diff_combine": [P, I, I, P, I, I, I, I, F, F, F, I, P],
         "acv_diff_attention_generic": [P, I, P, I, P, P, P, P, P, I, P, I, I, I, I, I, I, I, F, I, I, F, F, F, I, P],
         "acv_moe_route": [P, I, P, P, P, I, I, I, I, I, I, I, P, P, P, I, P],
         "acv_moe_group": [P, I, I, I, I, P, P, P, P, P],
@@ -705,7 +705,8 @@ def attention_decode(q: torch.Tensor, out: torch.Tensor, k_pages: torch.Tensor, 
         _p(q), q.stride(0), _p(out), out.stride(0), _p(k_pages), _p(v_pages), _p(dec_tokens), _p(dec_seqs), n_dec,
         _p(kv_len), _p(block_table), block_table.stride(0), _p(table_rows), num_heads, num_kv_heads, head_dim,
         k_pages.shape[2], k_pages.shape[0], scale, window, chunk, n_splits, _p(acc), _p(ml), _p(cnt), acc.numel(), ml.numel(), cnt.numel(),
-        max_kv or block_table.shape[1] * k_pages.shape[2], 1 if use_cluster else 0, _stream()), "attention_decode")
+        max_kv or block_table.shape[1] * k_pages.shape[2], 1 if use_cluster else 0,
+        1 if out.dtype == torch.float32 else 0, _stream()), "attention_decode")
     return out
 
 
@@ -718,8 +719,8 @@ def attention_chunk(q: torch.Tensor, out: torch.Tensor, k_pages: torch.Tensor, v
     _check(library().acv_attention_chunk(
         _p(q), q.stride(0), _p(out), out.stride(0), _p(k_pages), _p(v_pages), _p(tile_seq), _p(tile_q0), n_tiles,
         _p(cu_q), _p(kv_len), _p(block_table), block_table.stride(0), _p(table_rows), num_heads, num_kv_heads, head_dim,
-        k_pages.shape[2], k_pages.shape[0], scale, window, chunk, max_kv or block_table.shape[1] * k_pages.shape[2], _stream()),
-        "attention_chunk")
+        k_pages.shape[2], k_pages.shape[0], scale, window, chunk, 1 if out.dtype == torch.float32 else 0,
+        max_kv or block_table.shape[1] * k_pages.shape[2], _stream()), "attention_chunk")
     return out
 
 
@@ -732,12 +733,14 @@ def attention_tc(q: torch.Tensor, out: torch.Tensor, k_pages: torch.Tensor, v_pa
     _check(library().acv_attention_tc(
         _p(q), q.stride(0), q.shape[0], _p(out), out.stride(0), _p(k_pages), _p(v_pages), _p(tile_seq), _p(tile_q0),
         n_tiles, _p(cu_q), _p(kv_len), _p(block_table), block_table.stride(0), _p(table_rows), num_heads, num_kv_heads,
-        head_dim, k_pages.shape[2], k_pages.shape[0], scale, window, chunk, _p(status), _stream()), "attention_tc")
+        head_dim, k_pages.shape[2], k_pages.shape[0], scale, window, chunk, 1 if out.dtype == torch.float32 else 0, _p(status),
+        _stream()), "attention_tc")
     return out
 
 
 def attention_tc_takes(q: torch.Tensor, out: torch.Tensor, k_pages: torch.Tensor, head_dim: int) -> bool:
     page = k_pages.shape[2]
+    # (out may be float32 beside bfloat16 queries: the kernels then leave their result unrounded)
     return (head_dim in (64, 128) and page in (8, 16, 32, 64, 128) and q.stride(0) % 8 == 0 and out.stride(0) % 8 == 0
             and q.data_ptr() % 16 == 0 and out.data_ptr() % 16 == 0 and k_pages.is_contiguous())
 
@@ -1010,7 +1013,7 @@ def diff_combine(maps: torch.Tensor, out: torch.Tensor, num_heads: int, value_di
                  out_scale: float) -> torch.Tensor:
     """out[t, h] = unit_rms(maps[t, 2h] - lam * maps[t, 2h + 1]) * out_scale over the head's ``value_dim`` values."""
     _need_cuda(maps, out)
-    _check(library().acv_diff_combine(_p(maps), maps.stride(0), _p(out), out.stride(0), maps.shape[0], num_heads, value_dim,
+    _check(library().acv_diff_combine(_p(maps), maps.stride(0), 1 if maps.dtype == torch.float32 else 0, _p(out), out.stride(0), maps.shape[0], num_heads, value_dim,
                                       lam, eps, out_scale, dtype_code(out.dtype), _stream()), "diff_combine")
     return out
 

@@ -272,7 +272,8 @@ class DiffAttention(Mixer):
             wide = torch.empty((T, 2 * NH * 2 * D), device=h.device, dtype=h.dtype)
             ops.heads_norm_append(qkv, 2 * NH, 2 * NKV, NKV, D, DV, self.q_norm, self.k_norm, eps, ctx.positions,
                                   ctx.seq_of_token, *pages, table_rows=rows, q_out=wide)
-            maps = torch.empty((T, 2 * NH * DV), device=h.device, dtype=h.dtype)
+            # the maps leave the attention kernels as float: the difference of two nearly equal maps keeps its digits
+            maps = torch.empty((T, 2 * NH * DV), device=h.device, dtype=torch.float32)
             ops.attention(wide, maps, cache.k_pages, cache.v_pages, ctx, table, 2 * NH, NKV, 2 * D, self.scale, self.window,
                           work=work, chunk=self.chunk)
             ops.diff_combine(maps, out, NH, DV, self.lam, eps, 1.0 - self.diff)

@@ -106,7 +106,7 @@ class PagedCase:
             wide = torch.empty((T, 4 * NH * D), device=DEV, dtype=self.dtype)
             ops.heads_norm_append(qkv, 2 * NH, 2 * NKV, NKV, D, DV, qw, kw, self.eps, self.ctx.positions, self.ctx.seq_of_token,
                                   None, None, None, q_out=wide)
-            maps = torch.empty((T, 2 * NH * DV), device=DEV, dtype=self.dtype)
+            maps = torch.empty((T, 2 * NH * DV), device=DEV, dtype=torch.float32)
             ops.attention(wide, maps, self.k_pages, self.v_pages, self.ctx, self.table, 2 * NH, NKV, 2 * D, scale, window,
                           work=self.work, chunk=chunk)
             ops.diff_combine(maps, out, NH, DV, lam, self.eps, 1.0 - diff)
