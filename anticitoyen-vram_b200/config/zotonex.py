@@ -55,9 +55,9 @@ class ZotonexMixer:
         kv_from = m.get("kv_from")
         if kv_from is not None and (isinstance(kv_from, bool) or not isinstance(kv_from, int) or kv_from < 0):
             raise ConfigError(f"{where}'kv_from' must be a layer index, got {kv_from!r}")
-        heads = take_int(m, "heads")
-        self = cls(heads=heads, kv_heads=take_int(m, "kv_heads", heads), dim=take_int(m, "dim"), vdim=take_int(m, "vdim"),
-                   scale=take_float(m, "scale"), diff=take_float(m, "diff", positive=False),
+        heads, dim = take_int(m, "heads"), take_int(m, "dim")
+        self = cls(heads=heads, kv_heads=take_int(m, "kv_heads", heads), dim=dim, vdim=take_int(m, "vdim"),
+                   scale=take_float(m, "scale", dim ** -0.5), diff=take_float(m, "diff", positive=False),
                    mask_size=take_int(mask, "size") if mask else 0, kv_from=kv_from)
         if self.heads % self.kv_heads:
             raise ConfigError(f"{where}heads {self.heads} is not a multiple of kv_heads {self.kv_heads}")
