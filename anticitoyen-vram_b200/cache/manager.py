@@ -8,8 +8,11 @@ What a mixer keeps for a request is declared as a *need*:
   only the last ``window`` tokens are ever read again, so older pages go back to
   the pool as soon as the window has passed them; with ``chunk`` > 0 a token
   reads only the tokens of its own chunk of ``chunk`` positions (counted from
-  position 0), so the pages before the chunk of the next token go back.  A key
-  row (``head_dim`` elements) and a value row (``value_dim``) may differ in size.
+  position 0), so the pages before the chunk of the next token go back.  With
+  ``keep_first`` > 0 the first ``keep_first`` tokens of a request stay readable
+  behind the window, so the pages that hold them are never given back while the
+  request lives.  A key row (``head_dim`` elements) and a value row
+  (``value_dim``) may differ in size.
 * ``StateNeed``  - a tensor of fixed shape for each live request (a recurrent
   state), kept in a slot that is given at admission, zeroed, and taken back when
   the request ends.
@@ -73,6 +76,7 @@ class PagedNeed:
     window: int = 0
     value_dim: int = 0      # elements of a value row; 0: as many as a key row
     chunk: int = 0
+    keep_first: int = 0     # with a window: the first tokens of a request that every later token may still read
 
     @property
     def kind(self) -> str:
@@ -106,7 +110,7 @@ class PagedNeed:
         sizes, and whatever either of them may read again is kept (different rules of forgetting: everything)."""
         if (self.num_kv_heads, self.head_dim, self.value_size) != (other.num_kv_heads, other.head_dim, other.value_size):
             raise ValueError(f"{self} and {other} cannot share a cache slot: their rows differ")
-        if (self.window, self.chunk) == (other.window, other.chunk):
+        if (self.window, self.chunk, self.keep_first) == (other.window, other.chunk, other.keep_first):
             return self
         return PagedNeed(self.num_kv_heads, self.head_dim, 0, self.value_dim, 0)
 
@@ -265,7 +269,8 @@ class PagedGroup:
         table = self.tables[request]
         releasable = max(0, self.need.first_needed(kv_len) // self.page_size)
         releasable = min(releasable, len(table))
-        start = self.first_live[request]
+        # the pages of the kept first tokens stay; what the window has passed behind them goes
+        start = max(self.first_live[request], self.pages_for(self.need.keep_first) if self.need.window > 0 else 0)
         freed = [table[i] for i in range(start, releasable)]
         for i in range(start, releasable):
             table[i] = -1

@@ -1,12 +1,14 @@
 // Paged causal attention, generic form: any number of query tokens per request,
-// any head size in steps of 16 up to 256, float or bfloat16 pages.  One warp per
+// any head size up to 256 (value rows may have another size than key rows, DV != D), float or bfloat16 pages.  One warp per
 // (query token, query head).  It is the 32-bit path of the engine and the
 // fallback of the bfloat16 path for head sizes the tensor-core kernels do not take.
 //
 // Query-head h reads kv-head h / (NH/NKV) (acvram/engine/layers.py:1012-1017).
 // The keys of the step's own tokens are already in the pages, so the query at
 // absolute position p sees the keys j <= p, and with a window w > 0 only
-// j > p - w (mask aligned to absolute positions, acvram/engine/layers.py:1020-1041).
+// j > p - w (mask aligned to absolute positions, acvram/engine/layers.py:1020-1041); with keep_first = f > 0 the
+// first f keys of the request stay visible to every later query, whatever the window (they keep their own
+// positions: nothing is shifted).
 // s = scale * q.k; softmax over the visible keys with a running maximum and sum in
 // 32-bit (acvram/kernels/acvram_kernels.cu:993-1146 has the same recurrence).
 #include "common.cuh"
@@ -17,8 +19,8 @@ template <typename T, int NR>
 __global__ void attn_generic_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ out, int out_stride,
                                     const T* __restrict__ k_pages, const T* __restrict__ v_pages,
                                     const int* __restrict__ positions, const int* __restrict__ seq_of_token,
-                                    const int* __restrict__ block_table, int bt_stride, const int* __restrict__ bt_rows, int NH, int NKV, int D,
-                                    int page_size, int num_pages, float scale, int window) {
+                                    const int* __restrict__ block_table, int bt_stride, const int* __restrict__ bt_rows, int NH, int NKV, int D, int DV,
+                                    int page_size, int num_pages, float scale, int window, int keep_first) {
     extern __shared__ float sm_all[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int h = blockIdx.y * AG_WARPS + warp;
@@ -38,19 +40,23 @@ __global__ void attn_generic_kernel(const T* __restrict__ q, int q_stride, T* __
     for (int r = 0; r < NR; ++r) acc[r] = 0.f;
     float m = -INFINITY, l = 0.f;
     const int lo = window > 0 ? max(0, p - window + 1) : 0;
+    // two runs of keys: the kept first ones that the window has passed, [0, min(keep_first, lo)), then [lo, p]
+    const int kept = window > 0 ? min(max(keep_first, 0), lo) : 0;
 
-    for (int j0 = lo; j0 <= p; j0 += 32) {
+    for (int run = kept > 0 ? 0 : 1; run < 2; ++run) {
+    const int j_begin = run == 0 ? 0 : lo, j_last = run == 0 ? kept - 1 : p;
+    for (int j0 = j_begin; j0 <= j_last; j0 += 32) {
         const int j = j0 + lane;
-        bool valid = j <= p;
+        bool valid = j <= j_last;
         long long row = 0;
         if (valid) {
             const int pg = bt[j / page_size];
             valid = pg >= 0 && pg < num_pages;
-            row = (((long long)pg * NKV + kvh) * page_size + (j % page_size)) * D;
+            row = ((long long)pg * NKV + kvh) * page_size + (j % page_size);
         }
         float s = -INFINITY;
         if (valid) {
-            const T* kr = k_pages + row;
+            const T* kr = k_pages + row * D;
             float dot = 0.f;
             for (int e = 0; e < D; ++e) dot = fmaf(qs[e], to_f32(kr[e]), dot);
             s = dot;
@@ -64,41 +70,42 @@ __global__ void attn_generic_kernel(const T* __restrict__ q, int q_stride, T* __
         m = m_new;
 #pragma unroll
         for (int r = 0; r < NR; ++r) acc[r] *= alpha;
-        const int n_in_tile = min(32, p - j0 + 1);
+        const int n_in_tile = min(32, j_last - j0 + 1);
         for (int kk = 0; kk < n_in_tile; ++kk) {
             const float pk = __shfl_sync(0xffffffffu, pl, kk);
             const long long ro = __shfl_sync(0xffffffffu, row, kk);
             if (pk == 0.f) continue;
-            const T* vr = v_pages + ro;
+            const T* vr = v_pages + ro * DV;
 #pragma unroll
             for (int r = 0; r < NR; ++r) {
                 const int e = lane + 32 * r;
-                if (e < D) acc[r] = fmaf(pk, to_f32(vr[e]), acc[r]);
+                if (e < DV) acc[r] = fmaf(pk, to_f32(vr[e]), acc[r]);
             }
         }
     }
-    T* orow = out + (size_t)t * out_stride + (size_t)h * D;
+    }
+    T* orow = out + (size_t)t * out_stride + (size_t)h * DV;
     const float inv_l = l > 0.f ? 1.f / l : 0.f;
 #pragma unroll
     for (int r = 0; r < NR; ++r) {
         const int e = lane + 32 * r;
-        if (e < D) orow[e] = from_f32<T>(acc[r] * inv_l);
+        if (e < DV) orow[e] = from_f32<T>(acc[r] * inv_l);
     }
 }
 
 template <typename T>
 static int launch_generic(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,
                           const void* v_pages, const int* positions, const int* seq_of_token, const int* block_table,
-                          int bt_stride, const int* bt_rows, int T_tokens, int NH, int NKV, int D, int page_size, int num_pages,
-                          float scale, int window, cudaStream_t stream) {
+                          int bt_stride, const int* bt_rows, int T_tokens, int NH, int NKV, int D, int DV, int page_size, int num_pages,
+                          float scale, int window, int keep_first, cudaStream_t stream) {
     dim3 grid(T_tokens, (NH + AG_WARPS - 1) / AG_WARPS);
     const size_t smem = (size_t)AG_WARPS * D * sizeof(float);
-    const int nr = (D + 31) / 32;
+    const int nr = (DV + 31) / 32;
 #define AG_CASE(N)                                                                                                   \
     case N:                                                                                                          \
         attn_generic_kernel<T, N><<<grid, AG_WARPS * 32, smem, stream>>>(                                            \
             (const T*)q, q_stride, (T*)out, out_stride, (const T*)k_pages, (const T*)v_pages, positions,             \
-            seq_of_token, block_table, bt_stride, bt_rows, NH, NKV, D, page_size, num_pages, scale, window);                  \
+            seq_of_token, block_table, bt_stride, bt_rows, NH, NKV, D, DV, page_size, num_pages, scale, window, keep_first);                \
         break;
     switch (nr) {
         AG_CASE(1) AG_CASE(2) AG_CASE(3) AG_CASE(4) AG_CASE(5) AG_CASE(6) AG_CASE(7) AG_CASE(8)
@@ -112,16 +119,17 @@ ACV_API int acv_attention_generic(const void* q, int q_stride, void* out, int ou
                                   const void* v_pages, const int* positions, const int* seq_of_token,
                                   const int* block_table, int bt_stride, const int* bt_rows, int T_tokens, int NH, int NKV, int D,
                                   int page_size, int num_pages, float scale, int window, int dtype,
-                                  cudaStream_t stream) {
+                                  int value_dim, int keep_first, cudaStream_t stream) {
     if (T_tokens <= 0) return 0;
-    if (D <= 0 || D > 256 || NKV <= 0 || NH % NKV) return ACV_ERR_SIZE;
+    const int DV = value_dim > 0 ? value_dim : D;
+    if (D <= 0 || D > 256 || DV > 256 || NKV <= 0 || NH % NKV) return ACV_ERR_SIZE;
     if (dtype == ACV_F32)
         return launch_generic<float>(q, q_stride, out, out_stride, k_pages, v_pages, positions, seq_of_token,
-                                     block_table, bt_stride, bt_rows, T_tokens, NH, NKV, D, page_size, num_pages, scale, window,
-                                     stream);
+                                     block_table, bt_stride, bt_rows, T_tokens, NH, NKV, D, DV, page_size, num_pages, scale, window,
+                                     keep_first, stream);
     if (dtype == ACV_BF16)
         return launch_generic<bf16>(q, q_stride, out, out_stride, k_pages, v_pages, positions, seq_of_token,
-                                    block_table, bt_stride, bt_rows, T_tokens, NH, NKV, D, page_size, num_pages, scale, window,
-                                    stream);
+                                    block_table, bt_stride, bt_rows, T_tokens, NH, NKV, D, DV, page_size, num_pages, scale, window,
+                                    keep_first, stream);
     return ACV_ERR_DTYPE;
 }

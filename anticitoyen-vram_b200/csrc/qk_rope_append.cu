@@ -14,7 +14,11 @@
 //          acvram/kernels/acvram_kernels.cu:4496)
 // Pages are [num_pages, NKV, page_size, D].  Each step is optional (null weight,
 // null table, null pages), so that another position encoding can run between a
-// norm-only and an append-only launch.
+// norm-only and an append-only launch.  Value rows may have a size DV of their own
+// (the projection's row is then [NH*D | NKV*D | NKV*DV] and the value pages
+// [num_pages, NKV, page_size, DV]) and may be multiplied by a constant on their way
+// into the pages (a mixer whose output enters a weighted sum scales its values once
+// here, in float, as they are rounded into the pages, instead of its outputs later).
 #include "common.cuh"
 
 #define QRA_WARPS 8
@@ -25,19 +29,28 @@ __global__ void qk_norm_rope_append_kernel(T* __restrict__ qkv, int row_stride, 
                                            const float* __restrict__ cos_sin, int rot, int table_rows,
                                            const int* __restrict__ positions, const int* __restrict__ seq_of_token,
                                            const int* __restrict__ block_table, int bt_stride, const int* __restrict__ bt_rows, T* __restrict__ k_pages,
-                                           T* __restrict__ v_pages, int page_size, int num_pages) {
+                                           T* __restrict__ v_pages, int page_size, int num_pages, int DV, float v_scale) {
     extern __shared__ float sm_all[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int head = blockIdx.y * QRA_WARPS + warp;
     const int t = blockIdx.x;
     if (head >= NH + 2 * NKV) return;
-    float* sm = sm_all + warp * D;
-    T* src = qkv + (size_t)t * row_stride + (size_t)head * D;
+    float* sm = sm_all + warp * (D > DV ? D : DV);
     const bool is_q = head < NH;
     const bool is_k = !is_q && head < NH + NKV;
     const bool is_v = !is_q && !is_k;
+    T* src = qkv + (size_t)t * row_stride + (is_v ? (size_t)(NH + NKV) * D + (size_t)(head - NH - NKV) * DV : (size_t)head * D);
     const float* w = is_q ? q_w : (is_k ? k_w : nullptr);
     int pos = positions[t];
+    if (is_v) {      // a value row: copied (times the constant) into its page, nothing else
+        if (!k_pages) return;
+        const int seq = seq_of_token[t];
+        const int pg = block_table[(size_t)(bt_rows ? bt_rows[seq] : seq) * bt_stride + pos / page_size];
+        if (pg < 0 || pg >= num_pages) return;
+        T* dst = v_pages + (((size_t)pg * NKV + (head - NH - NKV)) * page_size + (pos % page_size)) * DV;
+        for (int e = lane; e < DV; e += 32) dst[e] = v_scale == 1.f ? src[e] : from_f32<T>(to_f32(src[e]) * v_scale);
+        return;
+    }
 
     float ss = 0.f;
     for (int e = lane; e < D; e += 32) {
@@ -173,8 +186,9 @@ ACV_API int acv_qk_norm_rope_append(void* qkv, int row_stride, int T, int NH, in
                                     const float* k_w, float eps, const float* cos_sin, int rot, int table_rows,
                                     const int* positions, const int* seq_of_token, const int* block_table,
                                     int bt_stride, const int* bt_rows, void* k_pages, void* v_pages, int page_size, int num_pages,
-                                    int dtype, cudaStream_t stream) {
+                                    int dtype, int value_dim, float v_scale, cudaStream_t stream) {
     if (T <= 0) return 0;
+    const int DV = value_dim > 0 ? value_dim : D;
     if (D <= 0 || D > 1024 || (cos_sin && (rot <= 0 || rot > D || (rot & 1)))) return ACV_ERR_SIZE;
     const int heads = NH + 2 * NKV;
     dim3 grid(T, (heads + QRA_WARPS - 1) / QRA_WARPS);
@@ -182,7 +196,7 @@ ACV_API int acv_qk_norm_rope_append(void* qkv, int row_stride, int T, int NH, in
     // vector form when a lane's elements make an aligned vector and the whole head rotates
     const int vec = D / 32;
     const size_t esz = dtype == ACV_F32 ? 4 : 2;
-    const bool vec_ok = D % 32 == 0 && (vec == 1 || vec == 2 || vec == 4 || vec == 8) && (!cos_sin || rot == D) &&
+    const bool vec_ok = DV == D && v_scale == 1.f && D % 32 == 0 && (vec == 1 || vec == 2 || vec == 4 || vec == 8) && (!cos_sin || rot == D) &&
                         vec * esz <= 16 && !((uintptr_t)qkv % (vec * esz)) && !((row_stride * esz) % (vec * esz)) &&
                         (!k_pages || (!((uintptr_t)k_pages % (vec * esz)) && !((uintptr_t)v_pages % (vec * esz))));
     if (vec_ok) {
@@ -199,15 +213,15 @@ ACV_API int acv_qk_norm_rope_append(void* qkv, int row_stride, int T, int NH, in
 #undef QRA_VEC
         return acv_launch_status();
     }
-    const size_t smem = (size_t)QRA_WARPS * D * sizeof(float);
+    const size_t smem = (size_t)QRA_WARPS * (D > DV ? D : DV) * sizeof(float);
     if (dtype == ACV_F32)
         qk_norm_rope_append_kernel<float><<<grid, QRA_WARPS * 32, smem, stream>>>(
             (float*)qkv, row_stride, NH, NKV, D, q_w, k_w, eps, cos_sin, rot, table_rows, positions, seq_of_token,
-            block_table, bt_stride, bt_rows, (float*)k_pages, (float*)v_pages, page_size, num_pages);
+            block_table, bt_stride, bt_rows, (float*)k_pages, (float*)v_pages, page_size, num_pages, DV, v_scale);
     else if (dtype == ACV_BF16)
         qk_norm_rope_append_kernel<bf16><<<grid, QRA_WARPS * 32, smem, stream>>>(
             (bf16*)qkv, row_stride, NH, NKV, D, q_w, k_w, eps, cos_sin, rot, table_rows, positions, seq_of_token,
-            block_table, bt_stride, bt_rows, (bf16*)k_pages, (bf16*)v_pages, page_size, num_pages);
+            block_table, bt_stride, bt_rows, (bf16*)k_pages, (bf16*)v_pages, page_size, num_pages, DV, v_scale);
     else
         return ACV_ERR_DTYPE;
     return acv_launch_status();

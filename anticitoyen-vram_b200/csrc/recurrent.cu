@@ -1,0 +1,208 @@
+// A gated linear recurrence over channels (the recurrent unit of Griffin-style blocks), for steps that mix
+// portions of prompts and single tokens.  For every request the step brings tokens cu_q[s] .. cu_q[s+1]-1; what
+// the request keeps between steps lies in state slots (float): the last K-1 inputs of the short convolution and
+// the recurrence's state, both zero when the request begins.
+//
+//   acv_causal_conv     u[t][c] = cb[c] + sum_j w[c][K-1-j] * (x[t-j][c] + xb[c])          j = 0 .. K-1, float
+//   acv_block_gates     r = sigmoid(A_b u_b + a_b),  g = sigmoid(B_b u_b + b_b)            per block b of the channels, float
+//   acv_gated_scan      a = exp(c_r * r * sp[c]);  S = a S + sqrt(1 - a^2) * g * u;  out = S * gelu_tanh(y + yb)
+//
+// sp[c] is softplus of the channel's decay parameter (folded when the weights are loaded), c_r the design's
+// constant (negative).  1 - a^2 is taken as -expm1(2 log a), which keeps its digits where a is close to 1.
+// Everything here is 32-bit; only the inputs x and y (a projection's output) and the result may have the run's
+// element type.
+#include "common.cuh"
+
+// ----------------------------------------------------------------------------- short causal convolution per channel
+// grid (tokens, channel tiles).  The tokens that reach back into the state (the first K-1 of a request's portion)
+// are all computed by the block of the portion's first token, which then replaces the state: each channel's
+// state is read and written by one thread only.
+template <typename T>
+__global__ void causal_conv_kernel(const T* __restrict__ x, int ldx, const float* __restrict__ xb,
+                                   const float* __restrict__ w, const float* __restrict__ cb, float* __restrict__ state,
+                                   const int* __restrict__ slots, const int* __restrict__ cu_q,
+                                   const int* __restrict__ seq_of_token, float* __restrict__ u, int C, int K) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t = blockIdx.x;
+    const int c = blockIdx.y * blockDim.x + threadIdx.x;
+    if (c >= C) return;
+    const int seq = seq_of_token[t];
+    const int first = cu_q[seq], len = cu_q[seq + 1] - first;
+    const int off = t - first;
+    const float bias_in = xb ? xb[c] : 0.f;
+    const float* wc = w + (size_t)c * K;
+    if (off >= K - 1) {
+        float acc = cb ? cb[c] : 0.f;
+        for (int j = 0; j < K; ++j) acc = fmaf(wc[K - 1 - j], to_f32(x[(size_t)(t - j) * ldx + c]) + bias_in, acc);
+        u[(size_t)t * C + c] = acc;
+        return;
+    }
+    if (off != 0) return;
+    float* st = state + (size_t)slots[seq] * (K - 1) * C;      // [K-1][C], the oldest input first
+    const int n_here = len < K - 1 ? len : K - 1;
+    for (int n = 0; n < n_here; ++n) {
+        float acc = cb ? cb[c] : 0.f;
+        for (int j = 0; j < K; ++j) {
+            const int src = n - j;
+            const float v = src >= 0 ? to_f32(x[(size_t)(first + src) * ldx + c]) + bias_in : st[(size_t)(K - 1 + src) * C + c];
+            acc = fmaf(wc[K - 1 - j], v, acc);
+        }
+        u[(size_t)(first + n) * C + c] = acc;
+    }
+    for (int i = 0; i < K - 1; ++i) {       // ascending: what is read lies behind what has been written
+        const int src = len - (K - 1) + i;
+        st[(size_t)i * C + c] = src >= 0 ? to_f32(x[(size_t)(first + src) * ldx + c]) + bias_in : st[(size_t)(len + i) * C + c];
+    }
+}
+
+ACV_API int acv_causal_conv(const void* x, int ldx, const float* xb, const float* w, const float* cb, float* state,
+                            const int* slots, const int* cu_q, const int* seq_of_token, float* u, int T, int C, int K,
+                            int dtype, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (C <= 0 || K < 1) return ACV_ERR_SIZE;
+    dim3 grid(T, (C + 127) / 128);
+    if (dtype == ACV_F32)
+        acv_launch(PDL_MISC, causal_conv_kernel<float>, grid, 128, 0, stream, (const float*)x, ldx, xb, w, cb, state, slots,
+                   cu_q, seq_of_token, u, C, K);
+    else if (dtype == ACV_BF16)
+        acv_launch(PDL_MISC, causal_conv_kernel<bf16>, grid, 128, 0, stream, (const bf16*)x, ldx, xb, w, cb, state, slots,
+                   cu_q, seq_of_token, u, C, K);
+    else
+        return ACV_ERR_DTYPE;
+    return acv_launch_status();
+}
+
+// ----------------------------------------------------------------------------- the two gates, block-diagonal
+// wa, wb: [blocks][in][out] (transposed when loaded, so that the threads of a warp read neighbouring outputs).
+// grid (token tiles of GT, blocks); a thread owns outputs o, o + blockDim, ... of its block for all tokens of the tile.
+#define GT 16
+
+__global__ void block_gates_kernel(const float* __restrict__ u, const float* __restrict__ wa, const float* __restrict__ ba,
+                                   const float* __restrict__ wb, const float* __restrict__ bb, float* __restrict__ r,
+                                   float* __restrict__ g, int T, int C, int BW) {
+    extern __shared__ float su[];          // [GT][BW]
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t0 = blockIdx.x * GT, blk = blockIdx.y;
+    const int nt = min(GT, T - t0);
+    for (int i = threadIdx.x; i < GT * BW; i += blockDim.x) {
+        const int tt = i / BW, e = i - tt * BW;
+        su[i] = tt < nt ? u[(size_t)(t0 + tt) * C + blk * BW + e] : 0.f;
+    }
+    __syncthreads();
+    const float* wa_b = wa + (size_t)blk * BW * BW;
+    const float* wb_b = wb + (size_t)blk * BW * BW;
+    for (int o = threadIdx.x; o < BW; o += blockDim.x) {
+        float ar[GT], ag[GT];
+#pragma unroll
+        for (int tt = 0; tt < GT; ++tt) ar[tt] = ag[tt] = 0.f;
+        for (int i = 0; i < BW; ++i) {
+            const float a = wa_b[(size_t)i * BW + o], b = wb_b[(size_t)i * BW + o];
+#pragma unroll
+            for (int tt = 0; tt < GT; ++tt) {
+                const float x = su[tt * BW + i];
+                ar[tt] = fmaf(a, x, ar[tt]);
+                ag[tt] = fmaf(b, x, ag[tt]);
+            }
+        }
+        const int ch = blk * BW + o;
+        const float b1 = ba ? ba[ch] : 0.f, b2 = bb ? bb[ch] : 0.f;
+#pragma unroll
+        for (int tt = 0; tt < GT; ++tt) {
+            if (tt < nt) {
+                r[(size_t)(t0 + tt) * C + ch] = 1.f / (1.f + expf(-(ar[tt] + b1)));
+                g[(size_t)(t0 + tt) * C + ch] = 1.f / (1.f + expf(-(ag[tt] + b2)));
+            }
+        }
+    }
+}
+
+ACV_API int acv_block_gates(const float* u, const float* wa, const float* ba, const float* wb, const float* bb, float* r,
+                            float* g, int T, int C, int blocks, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (blocks <= 0 || C % blocks) return ACV_ERR_SIZE;
+    const int BW = C / blocks;
+    const size_t smem = (size_t)GT * BW * sizeof(float);
+    if (smem > 200 * 1024) return ACV_ERR_SIZE;
+    if (smem > 48 * 1024) {
+        static AcvSmemConfig cfg;
+        const int e = acv_ensure_smem(cfg, block_gates_kernel, (int)smem);
+        if (e) return e;
+    }
+    dim3 grid((T + GT - 1) / GT, blocks);
+    const int threads = BW >= 256 ? 256 : (BW >= 128 ? 128 : (BW > 32 ? 64 : 32));
+    acv_launch(PDL_MISC, block_gates_kernel, grid, threads, smem, stream, u, wa, ba, wb, bb, r, g, T, C, BW);
+    return acv_launch_status();
+}
+
+// ----------------------------------------------------------------------------- the recurrence
+__device__ __forceinline__ float gelu_tanh_f32(float z) {
+    return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+}
+
+// grid (requests, channel tiles): a thread walks its channel through the request's tokens of this step; the loads of
+// SC tokens are issued before their recurrence runs, so that they do not wait for one another.
+#define SC 8
+
+template <typename TY, typename T>
+__global__ void gated_scan_kernel(const float* __restrict__ u, const float* __restrict__ r, const float* __restrict__ g,
+                                  const TY* __restrict__ y, int ldy, const float* __restrict__ yb,
+                                  const float* __restrict__ sp, float c_r, float* __restrict__ state,
+                                  const int* __restrict__ slots, const int* __restrict__ cu_q, T* __restrict__ out,
+                                  int ldo, int C) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int seq = blockIdx.x;
+    const int c = blockIdx.y * blockDim.x + threadIdx.x;
+    if (c >= C) return;
+    const int t0 = cu_q[seq], t1 = cu_q[seq + 1];
+    if (t1 <= t0) return;
+    float* st = state + (size_t)slots[seq] * C + c;
+    float S = *st;
+    const float rate = c_r * sp[c];
+    const float bias_y = yb ? yb[c] : 0.f;
+    for (int t = t0; t < t1; t += SC) {
+        float uu[SC], rr[SC], gg[SC], yy[SC];
+#pragma unroll
+        for (int i = 0; i < SC; ++i) {
+            const bool in = t + i < t1;
+            const size_t at = (size_t)(in ? t + i : t) * C + c;
+            uu[i] = u[at];
+            rr[i] = r[at];
+            gg[i] = g[at];
+            yy[i] = to_f32(y[(size_t)(in ? t + i : t) * ldy + c]);
+        }
+#pragma unroll
+        for (int i = 0; i < SC; ++i) {
+            if (t + i < t1) {
+                const float la = rate * rr[i];                 // log a <= 0
+                const float a = expf(la);
+                const float m = sqrtf(fmaxf(-expm1f(2.f * la), 0.f));
+                S = fmaf(a, S, m * gg[i] * uu[i]);
+                out[(size_t)(t + i) * ldo + c] = from_f32<T>(S * gelu_tanh_f32(yy[i] + bias_y));
+            }
+        }
+    }
+    *st = S;
+}
+
+ACV_API int acv_gated_scan(const float* u, const float* r, const float* g, const void* y, int ldy, const float* yb,
+                           const float* sp, float c_r, float* state, const int* slots, const int* cu_q, void* out, int ldo,
+                           int num_seqs, int C, int y_dtype, int dtype, cudaStream_t stream) {
+    if (num_seqs <= 0) return 0;
+    if (C <= 0) return ACV_ERR_SIZE;
+    dim3 grid(num_seqs, (C + 63) / 64);
+    if (y_dtype == ACV_F32 && dtype == ACV_F32)
+        acv_launch(PDL_MISC, gated_scan_kernel<float, float>, grid, 64, 0, stream, u, r, g, (const float*)y, ldy, yb, sp, c_r,
+                   state, slots, cu_q, (float*)out, ldo, C);
+    else if (y_dtype == ACV_F32 && dtype == ACV_BF16)
+        acv_launch(PDL_MISC, gated_scan_kernel<float, bf16>, grid, 64, 0, stream, u, r, g, (const float*)y, ldy, yb, sp, c_r,
+                   state, slots, cu_q, (bf16*)out, ldo, C);
+    else if (y_dtype == ACV_BF16 && dtype == ACV_BF16)
+        acv_launch(PDL_MISC, gated_scan_kernel<bf16, bf16>, grid, 64, 0, stream, u, r, g, (const bf16*)y, ldy, yb, sp, c_r,
+                   state, slots, cu_q, (bf16*)out, ldo, C);
+    else
+        return ACV_ERR_DTYPE;
+    return acv_launch_status();
+}

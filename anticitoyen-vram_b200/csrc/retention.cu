@@ -1,0 +1,207 @@
+// Retention: linear attention with a fixed decay per head, no softmax and no denominator.
+//
+//   S_t = decay_h * S_{t-1} + k_t v_t^T          S: [D, DV] per (request, head), float, kept in a state slot
+//   o_t = S_t^T q_t
+//
+// q and k are rotated by position (rotate-half over the first `rot` elements, cos and sin from a table) and k is
+// multiplied by k_scale, all in float, as they are staged; scores, state and sums are 32-bit.  A second kernel
+// brings each head's o to unit RMS (no weight), multiplies by silu(gate) and a constant, and rounds once.
+//
+// acv_retention: grid (requests, heads).  The block's threads are G groups of DV: thread (g, c) keeps rows
+// g*R .. g*R+R-1 of column c of S in registers, walks the request's tokens of this step in chunks of TC (q, k, v
+// staged in shared memory, the partial sums of the chunk reduced over the groups afterwards), and writes S back.
+#include "common.cuh"
+
+template <typename T, int R>
+__global__ void retention_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v, int ld,
+                                 const float* __restrict__ cos_sin, int rot, int table_rows,
+                                 const int* __restrict__ positions, const float* __restrict__ decay, float k_scale,
+                                 float* __restrict__ state, const int* __restrict__ slots,
+                                 const int* __restrict__ cu_q, float* __restrict__ o, int ldo, int H, int D, int DV,
+                                 int G, int TC) {
+    extern __shared__ float sm[];
+    float* qs = sm;                         // [TC][D]
+    float* ks = qs + (size_t)TC * D;        // [TC][D]
+    float* vs = ks + (size_t)TC * D;        // [TC][DV]
+    float* red = vs + (size_t)TC * DV;      // [TC][G][DV]
+    pdl_launch_dependents();
+    pdl_wait();
+    const int seq = blockIdx.x, h = blockIdx.y;
+    const int t0 = cu_q[seq], t1 = cu_q[seq + 1];
+    if (t1 <= t0) return;
+    const int tid = threadIdx.x, nthr = blockDim.x;
+    const int c = tid % DV, g = tid / DV;
+    const bool owner = g < G;
+    const float dec = decay[h];
+    float* st = state + ((size_t)slots[seq] * H + h) * D * DV;
+    float S[R];
+#pragma unroll
+    for (int i = 0; i < R; ++i) {
+        const int d = g * R + i;
+        S[i] = owner && d < D ? st[(size_t)d * DV + c] : 0.f;
+    }
+    const int half = rot >> 1;
+    for (int tb = t0; tb < t1; tb += TC) {
+        const int n = min(TC, t1 - tb);
+        for (int i = tid; i < n * D; i += nthr) {
+            const int tt = i / D, e = i - tt * D;
+            const size_t at = (size_t)(tb + tt) * ld + (size_t)h * D + e;
+            qs[i] = to_f32(q[at]);
+            ks[i] = to_f32(k[at]) * k_scale;
+        }
+        for (int i = tid; i < n * DV; i += nthr) {
+            const int tt = i / DV, e = i - tt * DV;
+            vs[i] = to_f32(v[(size_t)(tb + tt) * ld + (size_t)h * DV + e]);
+        }
+        __syncthreads();
+        if (cos_sin) {
+            for (int i = tid; i < n * half; i += nthr) {        // a pair (e, e + half) is turned by one thread
+                const int tt = i / half, e = i - tt * half;
+                const int pos = positions[tb + tt];
+                if (pos < 0 || pos >= table_rows) continue;
+                const float* cs = cos_sin + (size_t)pos * rot;
+                const float co = cs[e], si = cs[half + e];
+                float* a = qs + tt * D;
+                const float q0 = a[e], q1 = a[e + half];
+                a[e] = q0 * co - q1 * si;
+                a[e + half] = q1 * co + q0 * si;
+                a = ks + tt * D;
+                const float k0 = a[e], k1 = a[e + half];
+                a[e] = k0 * co - k1 * si;
+                a[e + half] = k1 * co + k0 * si;
+            }
+            __syncthreads();
+        }
+        if (owner) {
+            for (int tt = 0; tt < n; ++tt) {
+                const float vv = vs[tt * DV + c];
+                const float* kr = ks + tt * D + g * R;
+                const float* qr = qs + tt * D + g * R;
+                float part = 0.f;
+#pragma unroll
+                for (int i = 0; i < R; ++i) {
+                    if (g * R + i < D) {
+                        S[i] = fmaf(dec, S[i], kr[i] * vv);
+                        part = fmaf(S[i], qr[i], part);
+                    }
+                }
+                red[((size_t)tt * G + g) * DV + c] = part;
+            }
+        }
+        __syncthreads();
+        for (int i = tid; i < n * DV; i += nthr) {
+            const int tt = i / DV, e = i - tt * DV;
+            float sum = 0.f;
+            for (int gg = 0; gg < G; ++gg) sum += red[((size_t)tt * G + gg) * DV + e];
+            o[(size_t)(tb + tt) * ldo + (size_t)h * DV + e] = sum;
+        }
+        // the next chunk's staging writes qs, ks, vs only; its first barrier stands between this read of red and the
+        // next write of it
+    }
+    if (owner) {
+#pragma unroll
+        for (int i = 0; i < R; ++i) {
+            const int d = g * R + i;
+            if (d < D) st[(size_t)d * DV + c] = S[i];
+        }
+    }
+}
+
+template <typename T, int R>
+static int launch_retention(const void* q, const void* k, const void* v, int ld, const float* cos_sin, int rot,
+                            int table_rows, const int* positions, const float* decay, float k_scale, float* state,
+                            const int* slots, const int* cu_q, float* o, int ldo, int num_seqs, int H, int D, int DV,
+                            cudaStream_t stream) {
+    const int G = (D + R - 1) / R;
+    const int threads = ((G * DV + 31) / 32) * 32;
+    const size_t per_token = (size_t)(2 * D + DV + G * DV) * sizeof(float);
+    int TC = (int)((48 * 1024) / per_token);
+    TC = TC > 16 ? 16 : TC;
+    if (TC < 1) TC = 1;
+    const size_t smem = per_token * TC;
+    if (smem > 200 * 1024) return ACV_ERR_SIZE;
+    if (smem > 48 * 1024) {
+        static AcvSmemConfig cfg;
+        const int e = acv_ensure_smem(cfg, retention_kernel<T, R>, (int)smem);
+        if (e) return e;
+    }
+    acv_launch(PDL_ATTN, retention_kernel<T, R>, dim3(num_seqs, H), threads, smem, stream, (const T*)q, (const T*)k,
+               (const T*)v, ld, cos_sin, rot, table_rows, positions, decay, k_scale, state, slots, cu_q, o, ldo, H, D, DV, G, TC);
+    return acv_launch_status();
+}
+
+template <typename T>
+static int retention_by_rows(int R, const void* q, const void* k, const void* v, int ld, const float* cos_sin, int rot,
+                             int table_rows, const int* positions, const float* decay, float k_scale, float* state,
+                             const int* slots, const int* cu_q, float* o, int ldo, int num_seqs, int H, int D, int DV,
+                             cudaStream_t stream) {
+#define RET_CASE(N)                                                                                                  \
+    case N:                                                                                                          \
+        return launch_retention<T, N>(q, k, v, ld, cos_sin, rot, table_rows, positions, decay, k_scale, state, slots, \
+                                      cu_q, o, ldo, num_seqs, H, D, DV, stream);
+    switch (R) {
+        RET_CASE(4) RET_CASE(8) RET_CASE(16) RET_CASE(32) RET_CASE(64)
+    }
+#undef RET_CASE
+    return ACV_ERR_SIZE;
+}
+
+// q, k: rows of H*D at stride ld; v: rows of H*DV at stride ld; o: float rows of H*DV at stride ldo;
+// state: [slots][H][D][DV] float; decay: [H] float; cos_sin: [table_rows][rot] float or null.
+ACV_API int acv_retention(const void* q, const void* k, const void* v, int ld, const float* cos_sin, int rot,
+                          int table_rows, const int* positions, const float* decay, float k_scale, float* state,
+                          const int* slots, const int* cu_q, float* o, int ldo, int num_seqs, int H, int D, int DV,
+                          int dtype, cudaStream_t stream) {
+    if (num_seqs <= 0) return 0;
+    if (H <= 0 || D <= 0 || DV <= 0 || DV > 1024 || (cos_sin && (rot <= 0 || rot > D || (rot & 1)))) return ACV_ERR_SIZE;
+    int R = 4;
+    while (R <= 64 && ((D + R - 1) / R) * DV > 1024) R *= 2;
+    if (R > 64) return ACV_ERR_SIZE;
+    if (dtype == ACV_F32)
+        return retention_by_rows<float>(R, q, k, v, ld, cos_sin, rot, table_rows, positions, decay, k_scale, state, slots,
+                                        cu_q, o, ldo, num_seqs, H, D, DV, stream);
+    if (dtype == ACV_BF16)
+        return retention_by_rows<bf16>(R, q, k, v, ld, cos_sin, rot, table_rows, positions, decay, k_scale, state, slots,
+                                       cu_q, o, ldo, num_seqs, H, D, DV, stream);
+    return ACV_ERR_DTYPE;
+}
+
+// ----------------------------------------------------------------------------- unit RMS per head, gate, constant
+// out[t][h*DV + e] = o / sqrt(mean_e(o^2) + eps) * silu(gate) * out_scale; one warp per (token, head).
+template <typename T>
+__global__ void retention_gate_kernel(const float* __restrict__ o, int ldo, const T* __restrict__ gate, int ldg,
+                                      T* __restrict__ out, int ld_out, int H, int DV, float eps, float out_scale, int T_tokens) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int unit = blockIdx.x * (blockDim.x >> 5) + warp;
+    if (unit >= T_tokens * H) return;
+    const int t = unit / H, h = unit - t * H;
+    const float* orow = o + (size_t)t * ldo + (size_t)h * DV;
+    float ss = 0.f;
+    for (int e = lane; e < DV; e += 32) ss = fmaf(orow[e], orow[e], ss);
+    ss = warp_sum(ss);
+    const float inv = out_scale / sqrtf(ss / (float)DV + eps);
+    const T* grow = gate + (size_t)t * ldg + (size_t)h * DV;
+    T* dst = out + (size_t)t * ld_out + (size_t)h * DV;
+    for (int e = lane; e < DV; e += 32) {
+        const float z = to_f32(grow[e]);
+        dst[e] = from_f32<T>(orow[e] * inv * (z / (1.f + expf(-z))));
+    }
+}
+
+ACV_API int acv_retention_gate(const float* o, int ldo, const void* gate, int ldg, void* out, int ld_out, int T_tokens,
+                               int H, int DV, float eps, float out_scale, int dtype, cudaStream_t stream) {
+    if (T_tokens <= 0) return 0;
+    const int warps = 8;
+    const int grid = (T_tokens * H + warps - 1) / warps;
+    if (dtype == ACV_F32)
+        acv_launch(PDL_MISC, retention_gate_kernel<float>, grid, warps * 32, 0, stream, o, ldo, (const float*)gate, ldg,
+                   (float*)out, ld_out, H, DV, eps, out_scale, T_tokens);
+    else if (dtype == ACV_BF16)
+        acv_launch(PDL_MISC, retention_gate_kernel<bf16>, grid, warps * 32, 0, stream, o, ldo, (const bf16*)gate, ldg,
+                   (bf16*)out, ld_out, H, DV, eps, out_scale, T_tokens);
+    else
+        return ACV_ERR_DTYPE;
+    return acv_launch_status();
+}

@@ -62,7 +62,7 @@ class DecodeGraphs:
         r = self.runner
         m = r.manager
         padded = batch_bucket(len(entries))
-        pages = max(g.pages_for(s + 1) for g in m.paged_groups for s in starts)
+        pages = max((g.pages_for(s + 1) for g in m.paged_groups for s in starts), default=1)   # (a model may keep no pages)
         width = width_bucket(pages)
         key = (padded, width)
         slot = self.graphs.get(key)

@@ -69,8 +69,18 @@ def _declare(lib: ctypes.CDLL) -> None:
         "acv_add_rmsnorm": [P, P, P, P, P, I, I, F, I, P],
         "acv_swiglu": [P, P, I, I, I, P],
         "acv_add_bias": [P, I, P, I, I, I, P],
-        "acv_qk_norm_rope_append": [P, I, I, I, I, I, P, P, F, P, I, I, P, P, P, I, P, P, P, I, I, I, P],
-        "acv_attention_generic": [P, I, P, I, P, P, P, P, P, I, P, I, I, I, I, I, I, F, I, I, P],
+        "acv_qk_norm_rope_append": [P, I, I, I, I, I, P, P, F, P, I, I, P, P, P, I, P, P, P, I, I, I, I, F, P],
+        "acv_attention_generic": [P, I, P, I, P, P, P, P, P, I, P, I, I, I, I, I, I, F, I, I, I, I, P],
+        "acv_add_layernorm": [P, P, F, P, P, P, P, I, I, F, I, I, P],
+        "acv_token_shift": [P, P, P, P, P, P, P, I, I, I, P],
+        "acv_add_layernorm_shift": [P, P, F, P, P, P, P, P, P, I, I, F, I, I, P],
+        "acv_add_row_f32": [P, P, I, I, P],
+        "acv_softcap_f32": [P, LL, F, P],
+        "acv_causal_conv": [P, I, P, P, P, P, P, P, P, P, I, I, I, I, P],
+        "acv_block_gates": [P, P, P, P, P, P, P, I, I, I, P],
+        "acv_gated_scan": [P, P, P, P, I, P, P, F, P, P, P, P, I, I, I, I, I, P],
+        "acv_retention": [P, P, P, I, P, I, I, P, P, F, P, P, P, P, I, I, I, I, I, I, P],
+        "acv_retention_gate": [P, I, P, I, P, I, I, I, I, F, F, I, P],
         "acv_gemm_simt": [P, I, P, I, P, I, I, I, I, I, I, P],
         "acv_gemm_tc_qkv": [P, I, P, I, P, I, I, I, I, I, I, I, P, LL, P, LL, P, I, I, I, I, I, I, P, P, F, P, I, P, P, P, I, P, P, P, I, I, P],
         "acv_gemm_tc": [P, I, P, I, P, I, I, I, I, I, I, I, I, I, P, LL, P, LL, P, I, I, I, P],
@@ -257,11 +267,14 @@ def qk_norm_rope_append(qkv: torch.Tensor, num_heads: int, num_kv_heads: int, he
                         q_weight: torch.Tensor | None, k_weight: torch.Tensor | None, eps: float,
                         cos_sin: torch.Tensor | None, positions: torch.Tensor, seq_of_token: torch.Tensor,
                         block_table: torch.Tensor | None, k_pages: torch.Tensor | None,
-                        v_pages: torch.Tensor | None, table_rows: torch.Tensor | None = None) -> None:
+                        v_pages: torch.Tensor | None, table_rows: torch.Tensor | None = None, value_dim: int = 0,
+                        v_scale: float = 1.0) -> None:
     """Per-head norm, rotation and cache append over the stacked projection qkv [T, (NH+2NKV)*D], in place.
 
     cos_sin float32 [positions, R] (cos of R/2 angles, then sin); pages [NP, NKV, page, D].  ``table_rows``
-    (int32 [requests], optional): the row of ``block_table`` of each request of the batch (default: its index)."""
+    (int32 [requests], optional): the row of ``block_table`` of each request of the batch (default: its index).
+    ``value_dim`` > 0: value rows of that size (the row is [NH*D | NKV*D | NKV*value_dim], value pages
+    [NP, NKV, page, value_dim]); ``v_scale``: a constant on the values as they enter their pages."""
     _need_cuda(qkv)
     T = qkv.shape[0]
     rot = cos_sin.shape[1] if cos_sin is not None else 0
@@ -272,20 +285,22 @@ def qk_norm_rope_append(qkv: torch.Tensor, num_heads: int, num_kv_heads: int, he
     _check(library().acv_qk_norm_rope_append(
         _p(qkv), qkv.stride(0), T, num_heads, num_kv_heads, head_dim, _p(q_weight), _p(k_weight), eps, _p(cos_sin),
         rot, rows, _p(positions), _p(seq_of_token), _p(block_table), bts, _p(table_rows), _p(k_pages), _p(v_pages), page, n_pages,
-        dtype_code(qkv.dtype), _stream()), "qk_norm_rope_append")
+        dtype_code(qkv.dtype), int(value_dim), float(v_scale), _stream()), "qk_norm_rope_append")
 
 
 def attention_generic(q: torch.Tensor, out: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
                       positions: torch.Tensor, seq_of_token: torch.Tensor, block_table: torch.Tensor,
                       num_heads: int, num_kv_heads: int, head_dim: int, scale: float, window: int = 0,
-                      table_rows: torch.Tensor | None = None) -> torch.Tensor:
-    """Paged causal attention for every token of the step.  q: rows of num_heads*head_dim (row stride free)."""
+                      table_rows: torch.Tensor | None = None, value_dim: int = 0, keep_first: int = 0) -> torch.Tensor:
+    """Paged causal attention for every token of the step.  q: rows of num_heads*head_dim (row stride free).
+    ``value_dim`` > 0: value rows (and the result's heads) of that size; ``keep_first``: the first keys of a request
+    that stay visible behind the window."""
     _need_cuda(q, out, k_pages)
     T = q.shape[0]
     _check(library().acv_attention_generic(
         _p(q), q.stride(0), _p(out), out.stride(0), _p(k_pages), _p(v_pages), _p(positions), _p(seq_of_token),
         _p(block_table), block_table.stride(0), _p(table_rows), T, num_heads, num_kv_heads, head_dim, k_pages.shape[2],
-        k_pages.shape[0], scale, window, dtype_code(q.dtype), _stream()), "attention_generic")
+        k_pages.shape[0], scale, window, dtype_code(q.dtype), int(value_dim), int(keep_first), _stream()), "attention_generic")
     return out
 
 
@@ -791,10 +806,12 @@ def attention_work_decode(padded: int, max_kv: int) -> tuple[dict, dict]:
 
 def attention(qkv: torch.Tensor, out: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, ctx,
               block_table: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int, scale: float,
-              window: int = 0, work: dict | None = None, chunk: int = 0) -> torch.Tensor:
+              window: int = 0, work: dict | None = None, chunk: int = 0, value_dim: int = 0,
+              keep_first: int = 0) -> torch.Tensor:
     """Attention of every token of the step over its request's pages.  A query sees the keys at or before its
-    position; with ``window`` > 0 the last ``window`` of them; with ``chunk`` > 0 those of its own chunk of ``chunk``
-    positions counted from the request's position 0.
+    position; with ``window`` > 0 the last ``window`` of them, and with ``keep_first`` > 0 also the first
+    ``keep_first`` keys of the request; with ``chunk`` > 0 those of its own chunk of ``chunk``
+    positions counted from the request's position 0.  ``value_dim``: the size of a value row where it is not ``head_dim``.
 
     ``qkv`` is the stacked projection after norm and rotation (queries are its first
     num_heads*head_dim columns); ``ctx`` is the step's StepContext; ``work`` the step's work lists
@@ -802,11 +819,14 @@ def attention(qkv: torch.Tensor, out: torch.Tensor, k_pages: torch.Tensor, v_pag
     tensor-core kernels, requests with one token to the split-KV kernel and portions to the tiled
     one; everything else to the generic kernel."""
     rows = getattr(ctx, "table_rows", None)
-    if not tensor_core_attention_takes(qkv.dtype, num_heads, num_kv_heads, head_dim):
+    value_dim = value_dim or head_dim
+    keep_first = keep_first if window > 0 else 0
+    if value_dim != head_dim or keep_first > 0 or not tensor_core_attention_takes(qkv.dtype, num_heads, num_kv_heads, head_dim):
         if chunk > 0:
             raise KernelError("attention: the chunked mask is built for the tensor-core kernels' sizes only")
         return attention_generic(qkv, out, k_pages, v_pages, ctx.positions, ctx.seq_of_token, block_table, num_heads,
-                                 num_kv_heads, head_dim, scale, window, table_rows=rows)
+                                 num_kv_heads, head_dim, scale, window, table_rows=rows, value_dim=value_dim,
+                                 keep_first=keep_first)
     w = work if work is not None else ctx.work
     if w["n_dec"]:
         kv = min(w["max_dec_kv"], window) if window > 0 else w["max_dec_kv"]
@@ -1203,4 +1223,141 @@ def linear_bf16_glu(x: torch.Tensor, w_pairs: torch.Tensor, out: torch.Tensor, l
     _, _, status = _gemm_buffers(x.device, 0, 0)
     _check(library().acv_gemm_tc_glu(_p(x), x.stride(0), _p(w_pairs), w_pairs.stride(0), _p(out), out.stride(0), M, N, K, limit,
                                      alpha, bn, _p(status), sm_count(x.device), stages, mode | 2, _stream()), "gemm_tc_glu")
+    return out
+
+
+# ----------------------------------------------------------------------------- layer norm over a float stream, token shift
+def add_layernorm(x: torch.Tensor, delta: torch.Tensor | None, weight: torch.Tensor, bias: torch.Tensor | None, eps: float,
+                  out: torch.Tensor, rows: torch.Tensor | None = None, delta_scale: float = 1.0) -> torch.Tensor:
+    """x (float32 [T, H]) += delta_scale * delta in place (without ``rows``); out = (x - mean) / sqrt(var + eps) * w + b
+    in float, rounded once to out's type.  With ``rows`` (int32 [R]) only those rows, into out[0..R), x untouched."""
+    _need_cuda(x, out, weight)
+    if x.dtype != torch.float32 or not x.is_contiguous() or not out.is_contiguous() or (delta is not None and not delta.is_contiguous()):
+        raise KernelError("add_layernorm: a contiguous float32 stream and contiguous delta and output are wanted")
+    n = out.shape[0] if rows is not None else x.shape[0]
+    ddt = dtype_code(delta.dtype) if delta is not None else dtype_code(out.dtype)
+    _check(library().acv_add_layernorm(_p(x), _p(delta), float(delta_scale), _p(weight), _p(bias), _p(out), _p(rows), n,
+                                       x.shape[-1], eps, ddt, dtype_code(out.dtype), _stream()), "add_layernorm")
+    return out
+
+
+def token_shift(normed: torch.Tensor, mu: torch.Tensor, state: torch.Tensor, slots: torch.Tensor, cu_q: torch.Tensor,
+                seq_of_token: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[t] = n[t] + (n[t-1] - n[t]) * mu; the row before a request's first token of the step comes from
+    ``state[slots[request]]`` (float32 [slots, H]), which then takes the request's last row."""
+    _need_cuda(normed, mu, state, out)
+    if normed.dtype != torch.float32 or state.dtype != torch.float32 or not normed.is_contiguous() or not state.is_contiguous():
+        raise KernelError("token_shift: contiguous float32 rows and state are wanted")
+    T, H = normed.shape
+    _check(library().acv_token_shift(_p(normed), _p(mu), _p(state), _p(slots), _p(cu_q), _p(seq_of_token), _p(out), T, H,
+                                     dtype_code(out.dtype), _stream()), "token_shift")
+    return out
+
+
+def add_layernorm_shift(x: torch.Tensor, delta: torch.Tensor | None, weight: torch.Tensor, bias: torch.Tensor | None,
+                        eps: float, mu: torch.Tensor, state: torch.Tensor, slots: torch.Tensor, out: torch.Tensor,
+                        delta_scale: float = 1.0) -> torch.Tensor:
+    """``add_layernorm`` and ``token_shift`` in one launch, for a step in which row t is request t's only token."""
+    _need_cuda(x, out, weight, state)
+    if x.dtype != torch.float32 or not x.is_contiguous() or not out.is_contiguous() or not state.is_contiguous():
+        raise KernelError("add_layernorm_shift: a contiguous float32 stream, state and output are wanted")
+    ddt = dtype_code(delta.dtype) if delta is not None else dtype_code(out.dtype)
+    _check(library().acv_add_layernorm_shift(_p(x), _p(delta), float(delta_scale), _p(weight), _p(bias), _p(mu), _p(state),
+                                             _p(slots), _p(out), x.shape[0], x.shape[1], eps, ddt, dtype_code(out.dtype),
+                                             _stream()), "add_layernorm_shift")
+    return out
+
+
+def add_row_f32(x: torch.Tensor, row: torch.Tensor) -> torch.Tensor:
+    """x[t] += row for every row of the float32 stream x."""
+    _need_cuda(x, row)
+    if x.dtype != torch.float32 or row.dtype != torch.float32 or not x.is_contiguous() or row.numel() != x.shape[1]:
+        raise KernelError("add_row_f32: a contiguous float32 stream and a float32 vector of its width are wanted")
+    _check(library().acv_add_row_f32(_p(x), _p(row), x.shape[0], x.shape[1], _stream()), "add_row_f32")
+    return x
+
+
+def softcap_f32(x: torch.Tensor, cap: float) -> torch.Tensor:
+    """x <- cap * tanh(x / cap) in place (float32)."""
+    _need_cuda(x)
+    if x.dtype != torch.float32 or not x.is_contiguous():
+        raise KernelError("softcap_f32: a contiguous float32 tensor is wanted")
+    _check(library().acv_softcap_f32(_p(x), x.numel(), float(cap), _stream()), "softcap_f32")
+    return x
+
+
+# ----------------------------------------------------------------------------- gated linear recurrence
+def causal_conv(x: torch.Tensor, x_bias: torch.Tensor | None, taps: torch.Tensor, conv_bias: torch.Tensor | None,
+                state: torch.Tensor, slots: torch.Tensor, cu_q: torch.Tensor, seq_of_token: torch.Tensor,
+                out: torch.Tensor) -> torch.Tensor:
+    """out[t, c] = conv_bias[c] + sum_j taps[c, K-1-j] * (x[t-j, c] + x_bias[c]) over each request's tokens; what lies
+    before the step comes from ``state`` (float32 [slots, K-1, C], oldest first), which is replaced.  x: [T, C] view
+    (row stride free), out float32 [T, C]."""
+    _need_cuda(x, taps, state, out)
+    T, C = out.shape
+    K = taps.shape[1]
+    if out.dtype != torch.float32 or not out.is_contiguous() or x.stride(1) != 1 or taps.dtype != torch.float32 or not state.is_contiguous():
+        raise KernelError("causal_conv: float32 taps, state and output are wanted")
+    _check(library().acv_causal_conv(_p(x), x.stride(0), _p(x_bias), _p(taps), _p(conv_bias), _p(state), _p(slots), _p(cu_q),
+                                     _p(seq_of_token), _p(out), T, C, K, dtype_code(x.dtype), _stream()), "causal_conv")
+    return out
+
+
+def block_gates(u: torch.Tensor, wa_t: torch.Tensor, ba: torch.Tensor | None, wb_t: torch.Tensor, bb: torch.Tensor | None,
+                r: torch.Tensor, g: torch.Tensor) -> None:
+    """r = sigmoid(A_b u_b + ba), g = sigmoid(B_b u_b + bb) per block b of the channels; wa_t, wb_t float32
+    [blocks, in, out]; u, r, g float32 [T, C]."""
+    _need_cuda(u, wa_t, wb_t, r, g)
+    T, C = u.shape
+    if any(t.dtype != torch.float32 or not t.is_contiguous() for t in (u, wa_t, wb_t, r, g)):
+        raise KernelError("block_gates: contiguous float32 tensors are wanted")
+    _check(library().acv_block_gates(_p(u), _p(wa_t), _p(ba), _p(wb_t), _p(bb), _p(r), _p(g), T, C, wa_t.shape[0], _stream()),
+           "block_gates")
+
+
+def gated_scan(u: torch.Tensor, r: torch.Tensor, g: torch.Tensor, y: torch.Tensor, y_bias: torch.Tensor | None,
+               softplus_rate: torch.Tensor, c_r: float, state: torch.Tensor, slots: torch.Tensor, cu_q: torch.Tensor,
+               num_seqs: int, out: torch.Tensor) -> torch.Tensor:
+    """a = exp(c_r * r * softplus_rate); S = a S + sqrt(1 - a^2) g u per channel along each request's tokens, S from and
+    back to ``state`` (float32 [slots, C]); out[t] = S * gelu_tanh(y[t] + y_bias).  y: a [T, C] view, float32 or of
+    out's type; out: [T, C] of the run's type."""
+    _need_cuda(u, r, g, y, state, out)
+    C = u.shape[1]
+    if y.stride(1) != 1 or out.stride(1) != 1 or not state.is_contiguous():
+        raise KernelError("gated_scan: rows of y and out must be dense")
+    _check(library().acv_gated_scan(_p(u), _p(r), _p(g), _p(y), y.stride(0), _p(y_bias), _p(softplus_rate), float(c_r),
+                                    _p(state), _p(slots), _p(cu_q), _p(out), out.stride(0), num_seqs, C,
+                                    dtype_code(y.dtype), dtype_code(out.dtype), _stream()), "gated_scan")
+    return out
+
+
+# ----------------------------------------------------------------------------- retention
+def retention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cos_sin: torch.Tensor | None, positions: torch.Tensor,
+              decay: torch.Tensor, k_scale: float, state: torch.Tensor, slots: torch.Tensor, cu_q: torch.Tensor,
+              num_seqs: int, out: torch.Tensor, num_heads: int, dim: int, value_dim: int) -> torch.Tensor:
+    """S = decay_h S + k v^T, o = S^T q along each request's tokens, per head; q, k ([T, H*dim]) and v ([T, H*value_dim])
+    are views of one projection (same row stride); q and k are rotated by ``cos_sin`` (float32 [positions, rot]) and k
+    multiplied by ``k_scale`` in float; state float32 [slots, H, dim, value_dim]; out float32 [T, H*value_dim]."""
+    _need_cuda(q, k, v, state, out)
+    if not (q.stride(0) == k.stride(0) == v.stride(0)) or q.stride(1) != 1 or k.stride(1) != 1 or v.stride(1) != 1:
+        raise KernelError("retention: q, k and v must be views of one projection with dense rows")
+    if out.dtype != torch.float32 or state.dtype != torch.float32 or not state.is_contiguous() or out.stride(1) != 1:
+        raise KernelError("retention: float32 state and output are wanted")
+    rot = cos_sin.shape[1] if cos_sin is not None else 0
+    rows = cos_sin.shape[0] if cos_sin is not None else 0
+    _check(library().acv_retention(_p(q), _p(k), _p(v), q.stride(0), _p(cos_sin), rot, rows, _p(positions), _p(decay),
+                                   float(k_scale), _p(state), _p(slots), _p(cu_q), _p(out), out.stride(0), num_seqs,
+                                   num_heads, dim, value_dim, dtype_code(q.dtype), _stream()), "retention")
+    return out
+
+
+def retention_gate(o: torch.Tensor, gate: torch.Tensor, out: torch.Tensor, num_heads: int, value_dim: int, eps: float,
+                   out_scale: float = 1.0) -> torch.Tensor:
+    """out = o / sqrt(mean over a head of o^2 + eps) * silu(gate) * out_scale; o float32, gate and out views of the run's type."""
+    _need_cuda(o, gate, out)
+    if o.dtype != torch.float32 or gate.dtype != out.dtype or gate.stride(1) != 1 or out.stride(1) != 1 or o.stride(1) != 1:
+        raise KernelError("retention_gate: float32 o, and gate and out of one type with dense rows, are wanted")
+    _check(library().acv_retention_gate(_p(o), o.stride(0), _p(gate), gate.stride(0), _p(out), out.stride(0), o.shape[0],
+                                        num_heads, value_dim, eps, float(out_scale), dtype_code(out.dtype), _stream()),
+           "retention_gate")
     return out

@@ -38,6 +38,8 @@ class DecoderModel:
                 needs[block.prefix + name] = need
         for name, need in self.final_norm.tensor_needs().items():
             needs[plan.final_norm_prefix + name] = need
+        for name, shape in plan.stream_vectors.items():
+            needs[name] = TensorNeed(tuple(shape))
         # a tied head reads the embedding; a file that still carries the head's tensor is accepted
         needs[plan.head_name] = TensorNeed((plan.vocab_size, plan.hidden_size), "matrix", optional=plan.tied_head)
         return needs
@@ -51,6 +53,8 @@ class DecoderModel:
             block.load({n[len(p):]: t for n, t in tensors.items() if n.startswith(p)}, rt)
         p = plan.final_norm_prefix
         self.final_norm.load({n[len(p):]: t for n, t in tensors.items() if n.startswith(p)}, rt)
+        self.stream_vectors = {name: tensors[name].to(device=rt.device, dtype=torch.float32).contiguous()
+                               for name in plan.stream_vectors}
         if plan.tied_head:
             self.head = Linear(self.embedding)  # the same storage, no copy
         else:
@@ -79,7 +83,40 @@ class DecoderModel:
         return total
 
     # ------------------------------------------------------------------ cache
+    @staticmethod
+    def _leaves(need, path=()):
+        """(path, need) of every single need inside ``need``, which may be a dict of needs by name, nested."""
+        if isinstance(need, dict):
+            for name, sub in need.items():
+                yield from DecoderModel._leaves(sub, path + (name,))
+        elif need is not None:
+            yield path, need
+
     def cache_plan(self) -> CachePlan:
+        """One need for each thing that a scheduled run keeps.  A layer that keeps several things (pages beside a
+        state, say) names them; each becomes a slot of the cache manager, and ``self.slot_leaves`` remembers which
+        manager slots make up which of the plan's cache slots."""
+        composite = [None] * self.plan.num_cache_slots
+        for e in self.plan.schedule:
+            if e.cache >= 0 and isinstance(self.blocks[e.layer].cache_need(), dict):
+                if not e.writes or composite[e.cache] not in (None, e.layer):
+                    raise ValueError(f"cache slot {e.cache}: a layer that keeps several things shares its slot with no other run")
+                composite[e.cache] = e.layer
+        if any(c is not None for c in composite):
+            flat, self.slot_leaves = [], {}
+            for slot, layer in enumerate(composite):
+                if layer is None:
+                    need = next((self.blocks[e.layer].cache_need() for e in self.plan.schedule
+                                 if e.cache == slot and e.writes), None)
+                    self.slot_leaves[slot] = [((), len(flat))]
+                    flat.append(need)
+                    continue
+                self.slot_leaves[slot] = []
+                for path, need in self._leaves(self.blocks[layer].cache_need()):
+                    self.slot_leaves[slot].append((path, len(flat)))
+                    flat.append(need)
+            return CachePlan(flat)
+        self.slot_leaves = None
         needs = [None] * self.plan.num_cache_slots
         for e in self.plan.schedule:
             if e.cache < 0:
@@ -142,6 +179,33 @@ class DecoderModel:
                 out[key] = mixer
         return out
 
+    def _view(self, storage, slot: int, writes: bool) -> CacheView | None:
+        """The cache view of one manager slot."""
+        cplan = storage.manager.plan
+        g = cplan.group_of_slot[slot]
+        if g < 0:
+            return None
+        if cplan.groups[g].kind == "paged":
+            k, v = storage.pages(slot)
+            return CacheView(g, writes, k_pages=k, v_pages=v)
+        return CacheView(g, writes, state=storage.state(slot))
+
+    def _cache_view(self, storage, e) -> CacheView | None:
+        if e.cache < 0:
+            return None
+        if self.slot_leaves is None:
+            return self._view(storage, e.cache, e.writes)
+        leaves = self.slot_leaves[e.cache]
+        if len(leaves) == 1 and leaves[0][0] == ():
+            return self._view(storage, leaves[0][1], e.writes)
+        root = CacheView(-1, e.writes)
+        for path, slot in leaves:
+            node = root
+            for name in path[:-1]:
+                node = node.parts.setdefault(name, CacheView(-1, e.writes))
+            node.parts[path[-1]] = self._view(storage, slot, e.writes)
+        return root
+
     # ------------------------------------------------------------------ the step
     def forward(self, ctx, storage) -> torch.Tensor:
         """Run the step's tokens through every scheduled layer; logits float32 [R, V] at ctx.logit_rows."""
@@ -157,22 +221,27 @@ class DecoderModel:
             x = torch.empty((ctx.num_tokens, plan.hidden_size), device=rt.device, dtype=rt.dtype)
             ops.embed(self.embedding, ctx.tokens, x)
         delta = None
-        cplan = storage.manager.plan
+        if not hasattr(self, "slot_leaves"):
+            self.cache_plan()
+        mult = 1.0
         for e in plan.schedule:
-            view = None
-            if e.cache >= 0:
-                g = cplan.group_of_slot[e.cache]
-                if cplan.groups[g].kind == "paged":
-                    k, v = storage.pages(e.cache)
-                    view = CacheView(g, e.writes, k_pages=k, v_pages=v)
-                else:
-                    view = CacheView(g, e.writes, state=storage.state(e.cache))
-            x, delta = self.blocks[e.layer].forward(x, delta, ctx, view)
+            if e.stream_add is not None:
+                # a vector of the model joins the stream (the pending output of the layer before joins it later, in
+                # the next norm's kernel: the two sums commute)
+                name, row = e.stream_add
+                ops.add_row_f32(x, self.stream_vectors[name][row])
+            block = self.blocks[e.layer]
+            x, delta = block.forward(x, delta, ctx, self._cache_view(storage, e))
+            mult = getattr(block, "residual_mult", 1.0)
         if ctx.num_logit_rows == 0:
             return torch.empty((0, plan.vocab_size), device=rt.device, dtype=torch.float32)
         kw = {"out_dtype": rt.dtype} if x.dtype != rt.dtype else {}
+        if mult != 1.0:
+            kw["delta_scale"] = mult        # the last layer's output joins the stream with its block's factor
         h = self.final_norm.forward(x, delta, rows=ctx.logit_rows, **kw)
         logits = self.head(h, out_dtype=torch.float32)
         if plan.logit_scale != 1.0:
             ops.scale_f32(logits, plan.logit_scale)
+        if plan.logit_softcap > 0.0:
+            ops.softcap_f32(logits, plan.logit_softcap)
         return logits

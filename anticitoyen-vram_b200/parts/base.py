@@ -46,6 +46,9 @@ class CacheView:
     k_pages: torch.Tensor | None = None
     v_pages: torch.Tensor | None = None
     state: torch.Tensor | None = None   # [max_requests, *shape] for a StateNeed
+    # a part that keeps several things (pages beside a state, or parts side by side that each keep their own)
+    # names them in ``cache_need`` as a dict; its view then carries one view for each name here
+    parts: dict = field(default_factory=dict)
 
 
 class Part:
@@ -96,7 +99,8 @@ class Mixer(Part):
     metadata_key: str | None = None
 
     def cache_need(self):
-        """PagedNeed, StateNeed or None: what this mixer keeps for each request."""
+        """PagedNeed, StateNeed or None: what this mixer keeps for each request; or a dict {name: need} (needs may be
+        dicts again) where it keeps several things: its ``CacheView`` then has one view for each name in ``parts``."""
         return None
 
     def mixing_flops(self, q_lens, kv_lens) -> float:

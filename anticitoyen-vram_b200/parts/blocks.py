@@ -4,8 +4,11 @@ from __future__ import annotations
 
 import torch
 
+from ..cache.manager import StateNeed
 from ..kernels import ops
+from ..weights.needs import TensorNeed
 from .base import CacheView, Runtime
+from .norms import LayerNorm
 from .plan import LayerSpec
 from .registry import build, register
 
@@ -17,9 +20,21 @@ class PreNormBlock:
     The residual travels as (x, delta): the sum x + delta is made inside the next
     norm's kernel, as the reference's deferred-residual path does
     (acvram/engine/couches.py:427-443), so the stream is read and written once per
-    sub-block."""
+    sub-block.
+
+    Options (``LayerSpec.options``):
+      ``residual_mult`` m: x += m * mixer(...), x += m * feed_forward(...); the factor is applied inside the next norm's
+        kernel, in 32-bit, as the part's output joins the stream.
+      ``token_shift``: the name (behind the layer's prefix) of a vector mu of the stream's width.  What the mixer reads is
+        then h'[t] = h[t] + (h[t-1] - h[t]) * mu, h the first norm's output and h[t-1] the same of the request's previous
+        token (zeros before its first): the layer keeps one row of h for every request, in a state slot beside what its
+        mixer keeps, and the mix is made in 32-bit before h' is rounded to the parts' element type."""
 
     def __init__(self, spec: LayerSpec, hidden_size: int) -> None:
+        self.hidden_size = hidden_size
+        self.residual_mult = float(spec.options.get("residual_mult", 1.0))
+        self.token_shift = spec.options.get("token_shift")
+        self.shift_mu = None
         self.prefix = spec.prefix
         self.pre_mixer, self.pre_ff = spec.norm_prefixes
         self.input_norm = build("norm", spec.norm, hidden_size)
@@ -42,6 +57,8 @@ class PreNormBlock:
             for name, need in self.post_norm.tensor_needs().items():
                 needs[self.pre_ff + name] = need
             needs.update(self.feed_forward.tensor_needs())
+        if self.token_shift is not None:
+            needs[self.token_shift] = TensorNeed((self.hidden_size,))
         return needs
 
     def load(self, tensors, rt: Runtime) -> None:
@@ -52,9 +69,30 @@ class PreNormBlock:
         if self.feed_forward is not None:
             self.post_norm.load(sub(self.pre_ff), rt)
             self.feed_forward.load(tensors, rt)
+        if self.token_shift is not None:
+            self.shift_mu = tensors[self.token_shift].to(device=rt.device, dtype=torch.float32).contiguous()
 
     def cache_need(self):
-        return self.mixer.cache_need()
+        need = self.mixer.cache_need()
+        if self.token_shift is None:
+            return need
+        shift = StateNeed((self.hidden_size,), "float32")
+        return {"mixer": need, "shift": shift} if need is not None else {"shift": shift}
+
+    def _normed_shifted(self, x, delta, ctx, shift_view: CacheView, kw: dict, scale: dict):
+        """The first norm's output with the token shift applied, in the parts' element type."""
+        slots = ctx.state_slots[shift_view.group]
+        out_dtype = kw.get("out_dtype", x.dtype)
+        if ctx.max_q_len == 1 and ctx.num_tokens == ctx.num_seqs and isinstance(self.input_norm, LayerNorm) \
+                and x.dtype == torch.float32:
+            # every request brings one token: sum, norm, shift and the state's replacement in one launch
+            out = torch.empty((x.shape[0], x.shape[1]), device=x.device, dtype=out_dtype)
+            n = self.input_norm
+            return ops.add_layernorm_shift(x, delta, n.weight, n.bias, n.eps, self.shift_mu, shift_view.state, slots, out,
+                                           scale.get("delta_scale", 1.0))
+        normed = self.input_norm.forward(x, delta, out_dtype=torch.float32, **scale)
+        out = torch.empty(normed.shape, device=x.device, dtype=out_dtype)
+        return ops.token_shift(normed, self.shift_mu, shift_view.state, slots, ctx.cu_q, ctx.seq_of_token, out)
 
     def weight_bytes(self) -> int:
         return sum(p.weight_bytes() for p in (self.input_norm, self.post_norm, self.mixer, self.feed_forward) if p is not None)
@@ -103,9 +141,15 @@ class PreNormBlock:
                 return fused
         # a stream kept in float32 beside parts that run in bfloat16: the norms are told the parts' element type
         kw = {"out_dtype": self.run_dtype} if self.run_dtype is not None and x.dtype != self.run_dtype else {}
-        h = self.input_norm.forward(x, delta, **kw)
+        # (the pending output of the layer before belongs to a block of the same arrangement and factor)
+        scale = {"delta_scale": self.residual_mult} if self.residual_mult != 1.0 else {}
+        if self.token_shift is not None:
+            h = self._normed_shifted(x, delta, ctx, cache.parts["shift"], kw, scale)
+            cache = cache.parts.get("mixer")
+        else:
+            h = self.input_norm.forward(x, delta, **kw, **scale)
         a = self.mixer.forward(h, ctx, cache)
         if self.feed_forward is None:
             return x, a
-        h = self.post_norm.forward(x, a, **kw)
+        h = self.post_norm.forward(x, a, **kw, **scale)
         return x, self.feed_forward.forward(h, ctx)

@@ -16,17 +16,26 @@ class SwiGLU(FeedForward):
     """y = (silu(x Wg^T) * (x Wu^T)) Wd^T, gate and up as one stacked product
     (acvram/engine/attention.py:705-783)."""
 
-    def __init__(self, hidden_size: int, intermediate_size: int, prefix: str = "mlp.", bias: bool | None = None) -> None:
-        """``bias``: True, the three projections have biases; False, none; None, those that the file holds."""
+    def __init__(self, hidden_size: int, intermediate_size: int, prefix: str = "mlp.", bias: bool | None = None,
+                 names: dict | None = None) -> None:
+        """``bias``: True, the three projections have biases; False, none; None, those that the file holds.
+        ``names``: the tensors' names behind ``prefix``, {"gate": w, "gate.bias": b, "up": ..., "down": ...}."""
         self.hidden_size, self.intermediate_size = hidden_size, intermediate_size
         self.prefix = prefix
         self.bias = bias
+        if names is None:
+            names = {}
+            for role in ("gate", "up", "down"):
+                names[role], names[role + ".bias"] = f"{role}_proj.weight", f"{role}_proj.bias"
+        self.names = dict(names)
 
     def tensor_needs(self):
         H, I = self.hidden_size, self.intermediate_size
         needs = {}
-        for name, n_out, n_in in (("gate_proj.", I, H), ("up_proj.", I, H), ("down_proj.", H, I)):
-            needs.update(Linear.needs(self.prefix + name, n_out, n_in, self.bias))
+        for role, n_out, n_in in (("gate", I, H), ("up", I, H), ("down", H, I)):
+            needs[self.prefix + self.names[role]] = TensorNeed((n_out, n_in))
+            if self.bias is not False and role + ".bias" in self.names:
+                needs[self.prefix + self.names[role + ".bias"]] = TensorNeed((n_out,), "bias", optional=self.bias is None)
         return needs
 
     def weight_bytes(self) -> int:
@@ -36,10 +45,14 @@ class SwiGLU(FeedForward):
         return self.gate_up.flops(num_tokens) + self.down.flops(num_tokens)
 
     def load(self, tensors, rt: Runtime) -> None:
-        w = lambda n: tensors[n].to(device=rt.device, dtype=rt.dtype)
-        b = lambda n: tensors[n].to(device=rt.device, dtype=torch.float32) if n in tensors else None
-        gate, up = w(self.prefix + "gate_proj.weight"), w(self.prefix + "up_proj.weight")
-        gate_b, up_b, down_b = (b(self.prefix + n) for n in ("gate_proj.bias", "up_proj.bias", "down_proj.bias"))
+        w = lambda role: tensors[self.prefix + self.names[role]].to(device=rt.device, dtype=rt.dtype)
+
+        def b(role):
+            name = self.prefix + self.names.get(role + ".bias", "\0")
+            return tensors[name].to(device=rt.device, dtype=torch.float32) if name in tensors else None
+
+        gate, up = w("gate"), w("up")
+        gate_b, up_b, down_b = b("gate"), b("up"), b("down")
         # bfloat16 with 16-byte aligned rows: gate and up rows are interleaved (g0, u0, g1, u1 ...) so that the
         # tensor-core product's epilogue holds each pair together and applies SiLU(gate) * up itself; the
         # stacked product's output [T, 2I] is then never written.  Otherwise: stacked product, then the kernel.
@@ -49,7 +62,7 @@ class SwiGLU(FeedForward):
             self.gate_up = Linear(torch.stack([gate, up], dim=1).reshape(2 * self.intermediate_size, self.hidden_size))
         else:
             self.gate_up = Linear.stacked([gate, up], [gate_b, up_b])
-        self.down = Linear(w(self.prefix + "down_proj.weight"), down_b)
+        self.down = Linear(w("down"), down_b)
 
     def decode_layer_spec(self):
         """What the fused decode-layer kernel needs of this feed-forward: gate and up rows interleaved, no biases."""

@@ -1,4 +1,4 @@
-"""Token mixers.  Attention is the one this architecture has."""
+"""Token mixers over the paged cache: attention, differential attention, and two mixers side by side."""
 
 from __future__ import annotations
 
@@ -21,26 +21,47 @@ class Attention(Mixer):
     head_dim^-1/2 (acvram/engine/attention.py:149-151); ``window`` > 0 limits a query
     to the last ``window`` keys.  Tensor names are the Hugging Face ones, kept by the
     reference (acvram/engine/loader.py:1013-1023).  ``bias``: True, the four projections have
-    biases; False, none; None, those that the weight file holds (acvram/engine/loader.py:269-270)."""
+    biases; False, none; None, those that the weight file holds (acvram/engine/loader.py:269-270).
+
+    ``value_dim``: elements of a value vector (and of a head's output) where they differ from ``head_dim``.
+    ``keep_first`` > 0 (with a window): the first ``keep_first`` tokens of a request stay visible to every later query,
+    at their own positions.  ``names``: the four projections' tensor names behind ``prefix`` ({"q": name, ...}; biases
+    are then read only under names given as "q.bias" ...).  ``out_scale``: a constant on the mixer's output, for a mixer
+    whose output enters a weighted sum; it is applied to the values as they are written to their pages."""
+
+    ROLES = ("q", "k", "v", "o")
 
     def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int, position: PartSpec,
                  qk_norm_eps: float | None = None, scale: float | None = None, window: int = 0,
-                 prefix: str = "self_attn.", bias: bool | None = None) -> None:
+                 prefix: str = "self_attn.", bias: bool | None = None, value_dim: int | None = None, keep_first: int = 0,
+                 names: dict | None = None, out_scale: float = 1.0) -> None:
         if num_heads % num_kv_heads:
             raise ValueError(f"{num_heads} heads are not a multiple of {num_kv_heads} kv heads")
         self.hidden_size = hidden_size
         self.num_heads, self.num_kv_heads, self.head_dim = num_heads, num_kv_heads, head_dim
+        self.value_dim = int(value_dim) if value_dim else head_dim
         self.scale = float(scale) if scale is not None else head_dim ** -0.5
         self.qk_norm_eps = qk_norm_eps
         self.window = int(window)
+        self.keep_first = int(keep_first) if self.window > 0 else 0
+        self.out_scale = float(out_scale)
         self.prefix = prefix
         self.bias = bias
+        if names is None:
+            self.names = {r: f"{r}_proj.weight" for r in self.ROLES}
+            self.names.update({r + ".bias": f"{r}_proj.bias" for r in self.ROLES})
+        else:
+            self.names = dict(names)
         self.position = build("position", position, hidden_size)
         self.q_size = num_heads * head_dim
         self.kv_size = num_kv_heads * head_dim
+        self.v_size = num_kv_heads * self.value_dim
+        self.in_size = self.q_size + self.kv_size + self.v_size      # columns of the stacked input projection
+        self.inner_size = num_heads * self.value_dim                 # columns in front of the output projection
 
     def cache_need(self):
-        return PagedNeed(self.num_kv_heads, self.head_dim, self.window)
+        return PagedNeed(self.num_kv_heads, self.head_dim, self.window,
+                         self.value_dim if self.value_dim != self.head_dim else 0, 0, self.keep_first)
 
     # what the attention kernels want of a step beside the generic batch: their work lists.  One set serves every
     # attention layer of a model (the lists depend on the step's requests only), hence one key.
@@ -55,9 +76,11 @@ class Attention(Mixer):
     def tensor_needs(self):
         H = self.hidden_size
         needs = {}
-        for name, n_out, n_in in (("q_proj.", self.q_size, H), ("k_proj.", self.kv_size, H), ("v_proj.", self.kv_size, H),
-                                  ("o_proj.", H, self.q_size)):
-            needs.update(Linear.needs(self.prefix + name, n_out, n_in, self.bias))
+        for role, n_out, n_in in (("q", self.q_size, H), ("k", self.kv_size, H), ("v", self.v_size, H),
+                                  ("o", H, self.inner_size)):
+            needs[self.prefix + self.names[role]] = TensorNeed((n_out, n_in))
+            if self.bias is not False and role + ".bias" in self.names:
+                needs[self.prefix + self.names[role + ".bias"]] = TensorNeed((n_out,), "bias", optional=self.bias is None)
         if self.qk_norm_eps is not None:
             needs[self.prefix + "q_norm.weight"] = TensorNeed((self.head_dim,), "norm")
             needs[self.prefix + "k_norm.weight"] = TensorNeed((self.head_dim,), "norm")
@@ -66,12 +89,14 @@ class Attention(Mixer):
         return needs
 
     def load(self, tensors, rt: Runtime) -> None:
-        w = lambda n: tensors[n].to(device=rt.device, dtype=rt.dtype)
-        b = lambda n: tensors[n].to(device=rt.device, dtype=torch.float32) if n in tensors else None
-        self.qkv = Linear.stacked([w(self.prefix + "q_proj.weight"), w(self.prefix + "k_proj.weight"),
-                                   w(self.prefix + "v_proj.weight")],
-                                  [b(self.prefix + "q_proj.bias"), b(self.prefix + "k_proj.bias"), b(self.prefix + "v_proj.bias")])
-        self.o = Linear(w(self.prefix + "o_proj.weight"), b(self.prefix + "o_proj.bias"))
+        w = lambda r: tensors[self.prefix + self.names[r]].to(device=rt.device, dtype=rt.dtype)
+
+        def b(role):
+            name = self.prefix + self.names.get(role + ".bias", "\0")
+            return tensors[name].to(device=rt.device, dtype=torch.float32) if name in tensors else None
+
+        self.qkv = Linear.stacked([w("q"), w("k"), w("v")], [b("q"), b("k"), b("v")])
+        self.o = Linear(w("o"), b("o"))
         self.q_norm = self.k_norm = None
         if self.qk_norm_eps is not None:
             f = lambda n: tensors[n].to(device=rt.device, dtype=torch.float32).contiguous()
@@ -82,7 +107,8 @@ class Attention(Mixer):
         """What the fused decode-layer kernel needs of this mixer (it knows rotary positions over the whole head,
         applied by table, and no biases)."""
         rotary = self.position.rotary_table()
-        if self.qkv.bias is not None or self.o.bias is not None or rotary is None or rotary.shape[1] != self.head_dim:
+        if self.qkv.bias is not None or self.o.bias is not None or rotary is None or rotary.shape[1] != self.head_dim \
+                or self.value_dim != self.head_dim or self.keep_first or self.out_scale != 1.0:
             return None
         return {"num_heads": self.num_heads, "num_kv_heads": self.num_kv_heads, "head_dim": self.head_dim,
                 "window": self.window, "scale": self.scale, "w_qkv": self.qkv.weight, "w_o": self.o.weight,
@@ -90,9 +116,11 @@ class Attention(Mixer):
                 "metadata_key": self.metadata_key}
 
     # ---- cost of a step
+    def extra_weight_bytes(self) -> int:
+        return sum(t.numel() * 4 for t in (self.q_norm, self.k_norm) if t is not None)
+
     def weight_bytes(self) -> int:
-        norms = sum(t.numel() * 4 for t in (self.q_norm, self.k_norm) if t is not None)
-        return self.qkv.weight_bytes() + self.o.weight_bytes() + norms
+        return self.qkv.weight_bytes() + self.o.weight_bytes() + self.extra_weight_bytes()
 
     def flops(self, num_tokens: int) -> float:
         return self.qkv.flops(num_tokens) + self.o.flops(num_tokens)
@@ -102,17 +130,49 @@ class Attention(Mixer):
         full = q * (kv - q) + q * (q + 1) / 2
         if self.window <= 0:
             return full
-        return sum(min(self.window, kv - q + i + 1) for i in range(q))
+        # inside the window, plus the kept first keys that the window has passed
+        return sum(min(self.window, p + 1) + min(self.keep_first, max(0, p + 1 - self.window)) for p in range(kv - q, kv))
 
     def mixing_flops(self, q_lens, kv_lens) -> float:
-        return 4.0 * self.num_heads * self.head_dim * sum(self._seen(q, kv) for q, kv in zip(q_lens, kv_lens))
+        return 2.0 * self.num_heads * (self.head_dim + self.value_dim) * sum(self._seen(q, kv) for q, kv in zip(q_lens, kv_lens))
 
     def cache_bytes_read(self, q_lens, kv_lens, itemsize: int) -> int:
-        keys = sum(min(kv, self.window + q - 1) if self.window > 0 else kv for q, kv in zip(q_lens, kv_lens))
-        return 2 * keys * self.kv_size * itemsize
+        keys = sum(min(kv, self.window + q - 1 + self.keep_first) if self.window > 0 else kv for q, kv in zip(q_lens, kv_lens))
+        return keys * (self.kv_size + self.v_size) * itemsize
+
+    def mix(self, qkv, ctx, cache: CacheView, out) -> None:
+        """From the stacked projection ``qkv`` ([T, in_size], dense rows at any stride; its queries are changed in
+        place) to the heads' outputs ``out`` ([T, inner_size], likewise): norm, positions, append, attention."""
+        NH, NKV, D, DV = self.num_heads, self.num_kv_heads, self.head_dim, self.value_dim
+        table = ctx.block_tables[cache.group]
+        rows = ctx.table_rows
+        kp, vp = (cache.k_pages, cache.v_pages) if cache.writes else (None, None)
+        eps = self.qk_norm_eps if self.qk_norm_eps is not None else 0.0
+        rotary = self.position.rotary_table()
+        extra = {"value_dim": DV, "v_scale": self.out_scale} if (DV != D or self.out_scale != 1.0) else {}
+        if rotary is not None:
+            ops.qk_norm_rope_append(qkv, NH, NKV, D, self.q_norm, self.k_norm, eps, rotary, ctx.positions,
+                                    ctx.seq_of_token, table if kp is not None else None, kp, vp, table_rows=rows, **extra)
+        else:
+            if self.q_norm is not None:
+                ops.qk_norm_rope_append(qkv, NH, NKV, D, self.q_norm, self.k_norm, eps, None, ctx.positions,
+                                        ctx.seq_of_token, None, None, None, **extra)
+            T = qkv.shape[0]
+            self.position.apply(qkv[:, :self.q_size].unflatten(1, (NH, D)),
+                                qkv[:, self.q_size:self.q_size + self.kv_size].unflatten(1, (NKV, D)), ctx)
+            if kp is not None:
+                ops.qk_norm_rope_append(qkv, NH, NKV, D, None, None, 0.0, None, ctx.positions, ctx.seq_of_token,
+                                        table, kp, vp, table_rows=rows, **extra)
+        ops.attention(qkv, out, cache.k_pages, cache.v_pages, ctx, table, NH, NKV, D, self.scale, self.window,
+                      work=ctx.work[self.metadata_key], value_dim=DV, keep_first=self.keep_first)
 
     def forward(self, h, ctx, cache: CacheView):
         NH, NKV, D = self.num_heads, self.num_kv_heads, self.head_dim
+        if self.value_dim != D or self.out_scale != 1.0:
+            qkv = self.qkv(h)
+            out = torch.empty((qkv.shape[0], self.inner_size), device=h.device, dtype=h.dtype)
+            self.mix(qkv, ctx, cache, out)
+            return self.o(out)
         table = ctx.block_tables[cache.group]
         rows = ctx.table_rows
         kp, vp = (cache.k_pages, cache.v_pages) if cache.writes else (None, None)
@@ -141,7 +201,7 @@ class Attention(Mixer):
                                         table, kp, vp, table_rows=rows)
         out = torch.empty((qkv.shape[0], self.q_size), device=h.device, dtype=h.dtype)
         ops.attention(qkv, out, cache.k_pages, cache.v_pages, ctx, table, NH, NKV, D, self.scale, self.window,
-                      work=ctx.work[self.metadata_key])
+                      work=ctx.work[self.metadata_key], keep_first=self.keep_first)
         return self.o(out)
 
 
@@ -283,3 +343,76 @@ class DiffAttention(Mixer):
         ops.diff_attention(qkv, out, cache.k_pages, cache.v_pages, ctx, table, NH, NKV, D, DV, self.scale, self.lam, eps,
                            1.0 - self.diff, self.window, self.chunk, work=work)
         return self.o(out)
+
+
+@register("mixer", "parallel")
+class ParallelMixers(Mixer):
+    """Two mixers side by side over the same input; the result is the sum of their outputs (each mixer applies its own
+    constant, ``out_scale`` of its parameters, so that the sum is weighted).  Each keeps what it keeps: the cache view
+    has the parts "left" and "right".
+
+    Both sides must be mixers that can be driven from outside their projections: ``in_size``, ``inner_size``, ``qkv``
+    and ``o`` (their stacked input projection and their output projection) and ``mix(projected, ctx, cache, out)``.
+    The two input projections then run as one product over the shared input, and the two output projections as one
+    product over the heads' outputs laid side by side, [left | right] @ [W_left | W_right]^T, which is the sum."""
+
+    def __init__(self, hidden_size: int, left: PartSpec, right: PartSpec) -> None:
+        self.hidden_size = hidden_size
+        self.left = build("mixer", left, hidden_size)
+        self.right = build("mixer", right, hidden_size)
+        for side in (self.left, self.right):
+            if not all(hasattr(side, a) for a in ("in_size", "inner_size", "mix")):
+                raise ValueError(f"a '{side.kind}' mixer cannot stand beside another one (it offers no mix())")
+        keys = {k for k in (self.left.metadata_key, self.right.metadata_key) if k is not None}
+        if len(keys) > 1:
+            raise ValueError("mixers side by side may ask for one kind of per-step data between them")
+        self.metadata_key = keys.pop() if keys else None
+        self._provider = self.left if self.left.metadata_key is not None else self.right
+
+    def step_metadata(self, q_lens, kv_lens, cu_q) -> StepMetadata:
+        return self._provider.step_metadata(q_lens, kv_lens, cu_q)
+
+    def decode_metadata(self, padded: int, max_kv: int) -> StepMetadata:
+        return self._provider.decode_metadata(padded, max_kv)
+
+    def cache_need(self):
+        needs = {"left": self.left.cache_need(), "right": self.right.cache_need()}
+        return {k: v for k, v in needs.items() if v is not None} or None
+
+    def tensor_needs(self):
+        return {**self.left.tensor_needs(), **self.right.tensor_needs()}
+
+    def load(self, tensors, rt: Runtime) -> None:
+        self.left.load(tensors, rt)
+        self.right.load(tensors, rt)
+        l, r = self.left, self.right
+        self.inp = Linear.stacked([l.qkv.weight, r.qkv.weight], [l.qkv.bias, r.qkv.bias])
+        if (l.o.bias is None) != (r.o.bias is None):
+            bias = (l.o.bias if l.o.bias is not None else r.o.bias)
+        else:
+            bias = l.o.bias + r.o.bias if l.o.bias is not None else None
+        self.o = Linear(torch.cat([l.o.weight, r.o.weight], dim=1), bias)
+        # the sides' own copies of the stacked weights are not read again
+        l.qkv = l.o = r.qkv = r.o = None
+
+    def weight_bytes(self) -> int:
+        # the sides' projections are the two stacked products here; what else a side reads (norm weights) it reports itself
+        extra = sum(getattr(side, "extra_weight_bytes", lambda: 0)() for side in (self.left, self.right))
+        return self.inp.weight_bytes() + self.o.weight_bytes() + extra
+
+    def flops(self, num_tokens: int) -> float:
+        return self.inp.flops(num_tokens) + self.o.flops(num_tokens)
+
+    def mixing_flops(self, q_lens, kv_lens) -> float:
+        return self.left.mixing_flops(q_lens, kv_lens) + self.right.mixing_flops(q_lens, kv_lens)
+
+    def cache_bytes_read(self, q_lens, kv_lens, itemsize: int) -> int:
+        return self.left.cache_bytes_read(q_lens, kv_lens, itemsize) + self.right.cache_bytes_read(q_lens, kv_lens, itemsize)
+
+    def forward(self, h, ctx, cache: CacheView):
+        l, r = self.left, self.right
+        proj = self.inp(h)
+        inner = torch.empty((h.shape[0], l.inner_size + r.inner_size), device=h.device, dtype=h.dtype)
+        l.mix(proj[:, :l.in_size], ctx, cache.parts.get("left"), inner[:, :l.inner_size])
+        r.mix(proj[:, l.in_size:], ctx, cache.parts.get("right"), inner[:, l.inner_size:])
+        return self.o(inner)

@@ -1,4 +1,4 @@
-"""RMS norm with the residual sum fused in."""
+"""Norms with the residual sum fused in."""
 
 from __future__ import annotations
 
@@ -45,3 +45,41 @@ class RMSNorm(Norm):
         if x.dtype == torch.float32 and out_dtype != torch.float32:
             return ops.add_rmsnorm_f32(x, delta, self.weight, self.eps, out, rows)
         return ops.add_rmsnorm(x, delta, self.weight, self.eps, out, rows)
+
+
+@register("norm", "layernorm")
+class LayerNorm(Norm):
+    """out = (x - mean) / sqrt(var + eps) * w + b over a float32 residual stream, var the mean of the squared
+    deviations; the sum x += delta_scale * delta is made first, in 32-bit, and written back.  Mean, variance and the
+    affine step are 32-bit in every run precision; the result is rounded once to the parts' element type.
+    ``tensor`` and ``bias_tensor``: the names of w and b behind the norm's prefix (``bias_tensor`` None: no b)."""
+
+    def __init__(self, hidden_size: int, eps: float, size: int | None = None, tensor: str = "weight",
+                 bias_tensor: str | None = "bias") -> None:
+        self.size = size or hidden_size
+        self.eps = float(eps)
+        self.tensor, self.bias_tensor = tensor, bias_tensor
+        self.weight: torch.Tensor | None = None
+        self.bias: torch.Tensor | None = None
+
+    def tensor_needs(self):
+        needs = {self.tensor: TensorNeed((self.size,), "norm")}
+        if self.bias_tensor is not None:
+            needs[self.bias_tensor] = TensorNeed((self.size,), "bias")
+        return needs
+
+    def load(self, tensors, rt: Runtime) -> None:
+        f = lambda n: tensors[n].to(device=rt.device, dtype=torch.float32).contiguous()
+        self.weight = f(self.tensor)
+        self.bias = f(self.bias_tensor) if self.bias_tensor is not None else None
+
+    def weight_bytes(self) -> int:
+        return sum(t.numel() * 4 for t in (self.weight, self.bias) if t is not None)
+
+    def forward(self, x, delta, rows=None, out_dtype=None, delta_scale: float = 1.0):
+        if x.dtype != torch.float32:
+            raise ValueError("the layer norm is built for a float32 residual stream (ModelPlan.residual_dtype)")
+        n = rows.shape[0] if rows is not None else x.shape[0]
+        out_dtype = out_dtype or (delta.dtype if delta is not None else x.dtype)
+        out = torch.empty((n, x.shape[1]), device=x.device, dtype=out_dtype)
+        return ops.add_layernorm(x, delta, self.weight, self.bias, self.eps, out, rows, delta_scale)

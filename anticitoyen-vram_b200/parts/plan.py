@@ -33,6 +33,7 @@ class LayerSpec:
     feed_forward: PartSpec | None   # None: the layer is its mixer alone (no second norm either)
     norm: PartSpec       # the norm placed before the mixer and before the feed-forward
     norm_prefixes: tuple[str, str] = ("input_layernorm.", "post_attention_layernorm.")
+    options: Mapping[str, Any] = field(default_factory=dict)    # parameters of the block arrangement itself
 
 
 @dataclass(frozen=True)
@@ -43,6 +44,9 @@ class ScheduleEntry:
     layer: int
     cache: int
     writes: bool = True
+    # (tensor name, row): that row of a [rows, hidden] tensor of the model joins the stream before this run
+    # (a repeated stretch of layers that tells its passes apart by a vector of their own)
+    stream_add: tuple[str, int] | None = None
 
 
 @dataclass(frozen=True)
@@ -64,6 +68,9 @@ class ModelPlan:
     # "float32": the residual stream is float32 in every run precision (the sums x + delta are then never rounded to
     # bfloat16); None: the stream has the run's element type
     residual_dtype: str | None = None
+    logit_softcap: float = 0.0        # > 0: logits <- cap * tanh(logits / cap)
+    # tensors of the model beside its layers', {name: shape}: what ``ScheduleEntry.stream_add`` names lives here
+    stream_vectors: Mapping[str, tuple] = field(default_factory=dict)
 
     @property
     def num_cache_slots(self) -> int:

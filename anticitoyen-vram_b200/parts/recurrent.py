@@ -1,0 +1,195 @@
+"""Token mixers that keep a state of fixed size for each request instead of pages: retention and a gated
+linear recurrence.  Their states are 32-bit in every run precision and live in the cache manager's state slots
+(zeroed when a request begins); a step may bring any mix of portions of prompts and single tokens."""
+
+from __future__ import annotations
+
+import math
+
+import torch
+
+from ..cache.manager import StateNeed
+from ..kernels import ops
+from ..weights.needs import TensorNeed
+from .base import CacheView, Mixer, Runtime
+from .linear import Linear
+from .plan import PartSpec
+from .registry import build, register
+
+
+@register("mixer", "retention")
+class Retention(Mixer):
+    """Linear attention with a fixed decay per head, without softmax or denominator:
+
+        S_t = decay_h S_{t-1} + k_t v_t^T,   o_t = S_t^T q_t            S: [dim, value_dim] per head, float32
+
+    q and k get the position encoding (``position``; None: none), k is then multiplied by ``k_scale`` (default
+    dim^-1/2).  Each head's o is brought to unit RMS (``norm_eps``, no weight), the heads side by side are multiplied
+    by silu(W_g h) and by ``out_scale``, and projected by W_o.  Tensors behind ``prefix``: q, k, v, g, o (``names``
+    renames them); no biases."""
+
+    NAMES = {n: n for n in ("q", "k", "v", "g", "o")}
+
+    def __init__(self, hidden_size: int, num_heads: int, dim: int, value_dim: int, decay, norm_eps: float,
+                 position: PartSpec | None = None, k_scale: float | None = None, prefix: str = "mix.",
+                 names: dict | None = None, out_scale: float = 1.0) -> None:
+        decay = [float(d) for d in decay]
+        if len(decay) != num_heads:
+            raise ValueError(f"{len(decay)} decays for {num_heads} heads")
+        self.hidden_size = hidden_size
+        self.num_heads, self.dim, self.value_dim = num_heads, dim, value_dim
+        self.decay_values = decay
+        self.norm_eps = float(norm_eps)
+        self.k_scale = float(k_scale) if k_scale is not None else dim ** -0.5
+        self.out_scale = float(out_scale)
+        self.prefix = prefix
+        self.names = {**self.NAMES, **(names or {})}
+        self.position = build("position", position, hidden_size) if position is not None else None
+        self.qk_size = num_heads * dim
+        self.inner_size = num_heads * value_dim
+        self.in_size = 2 * self.qk_size + 2 * self.inner_size        # [q | k | v | g]
+
+    def _n(self, role: str) -> str:
+        return self.prefix + self.names[role]
+
+    def cache_need(self):
+        return StateNeed((self.num_heads, self.dim, self.value_dim), "float32")
+
+    def tensor_needs(self):
+        H = self.hidden_size
+        return {self._n("q"): TensorNeed((self.qk_size, H)), self._n("k"): TensorNeed((self.qk_size, H)),
+                self._n("v"): TensorNeed((self.inner_size, H)), self._n("g"): TensorNeed((self.inner_size, H)),
+                self._n("o"): TensorNeed((H, self.inner_size))}
+
+    def load(self, tensors, rt: Runtime) -> None:
+        w = lambda role: tensors[self._n(role)].to(device=rt.device, dtype=rt.dtype)
+        self.qkv = Linear.stacked([w("q"), w("k"), w("v"), w("g")])
+        self.o = Linear(w("o"))
+        self.decay = torch.tensor(self.decay_values, dtype=torch.float32, device=rt.device)
+        if self.position is not None:
+            self.position.load({}, rt)
+            if self.position.rotary_table() is None:
+                raise ValueError("retention takes a position encoding that offers a rotary table")
+
+    def extra_weight_bytes(self) -> int:
+        return 0
+
+    def weight_bytes(self) -> int:
+        return self.qkv.weight_bytes() + self.o.weight_bytes()
+
+    def flops(self, num_tokens: int) -> float:
+        return self.qkv.flops(num_tokens) + self.o.flops(num_tokens)
+
+    def mixing_flops(self, q_lens, kv_lens) -> float:
+        # per token and head: the state's update and its product with q
+        return 4.0 * self.num_heads * self.dim * self.value_dim * sum(q_lens)
+
+    def cache_bytes_read(self, q_lens, kv_lens, itemsize: int) -> int:
+        return len(q_lens) * self.num_heads * self.dim * self.value_dim * 4
+
+    def mix(self, proj, ctx, cache: CacheView, out) -> None:
+        H, D, DV = self.num_heads, self.dim, self.value_dim
+        a, b = self.qk_size, 2 * self.qk_size
+        o = torch.empty((proj.shape[0], self.inner_size), device=proj.device, dtype=torch.float32)
+        table = self.position.rotary_table() if self.position is not None else None
+        ops.retention(proj[:, :a], proj[:, a:b], proj[:, b:b + self.inner_size], table, ctx.positions, self.decay,
+                      self.k_scale, cache.state, ctx.state_slots[cache.group], ctx.cu_q, ctx.num_seqs, o, H, D, DV)
+        ops.retention_gate(o, proj[:, b + self.inner_size:], out, H, DV, self.norm_eps, self.out_scale)
+
+    def forward(self, h, ctx, cache: CacheView):
+        proj = self.qkv(h)
+        out = torch.empty((h.shape[0], self.inner_size), device=h.device, dtype=h.dtype)
+        self.mix(proj, ctx, cache, out)
+        return self.o(out)
+
+
+@register("mixer", "rglru")
+class GatedLinearRecurrence(Mixer):
+    """The recurrent block of Griffin (De et al., "Griffin: Mixing Gated Linear Recurrences with Local Attention for
+    Efficient Language Models"): two branches of ``width`` channels,
+
+        y = gelu_tanh(W_y h + b_y)
+        u = conv(W_x h + b_x)               a causal convolution of ``conv`` taps per channel, the last tap the current token's
+        r = sigmoid(A_b u_b + a_b),  g = sigmoid(B_b u_b + b_b)        per block b of ``blocks`` equal parts of the channels
+        a = exp(-rate * r * softplus(lam)),   S_t = a S_{t-1} + sqrt(1 - a^2) * g * u          (S_{-1} = 0)
+        out = W_o (S * y)
+
+    What a request keeps: the last ``conv`` - 1 inputs of the convolution and S, both float32.  Gates, decays and the
+    recurrence are 32-bit in every run precision; the two input projections leave their product as float32.
+    Tensors behind ``prefix``: y, y.b, x, x.b, conv, conv.b, ra, ra.b, ri, ri.b, lam, o."""
+
+    NAMES = {n: n for n in ("y", "y.b", "x", "x.b", "conv", "conv.b", "ra", "ra.b", "ri", "ri.b", "lam", "o")}
+
+    def __init__(self, hidden_size: int, width: int, blocks: int, conv: int, rate: float = 8.0, prefix: str = "mix.",
+                 names: dict | None = None) -> None:
+        if width % blocks:
+            raise ValueError(f"{width} channels do not split into {blocks} equal blocks")
+        if conv < 1:
+            raise ValueError("the convolution has at least one tap")
+        self.hidden_size, self.width, self.blocks, self.taps, self.rate = hidden_size, width, blocks, conv, float(rate)
+        self.prefix = prefix
+        self.names = {**self.NAMES, **(names or {})}
+
+    def _n(self, role: str) -> str:
+        return self.prefix + self.names[role]
+
+    def cache_need(self):
+        needs = {"state": StateNeed((self.width,), "float32")}
+        if self.taps > 1:
+            needs["conv"] = StateNeed((self.taps - 1, self.width), "float32")
+        return needs
+
+    def tensor_needs(self):
+        H, C, B = self.hidden_size, self.width, self.blocks
+        bw = C // B
+        return {self._n("y"): TensorNeed((C, H)), self._n("y.b"): TensorNeed((C,), "bias"),
+                self._n("x"): TensorNeed((C, H)), self._n("x.b"): TensorNeed((C,), "bias"),
+                self._n("conv"): TensorNeed((C, self.taps)), self._n("conv.b"): TensorNeed((C,), "bias"),
+                self._n("ra"): TensorNeed((B, bw, bw)), self._n("ra.b"): TensorNeed((B, bw), "bias"),
+                self._n("ri"): TensorNeed((B, bw, bw)), self._n("ri.b"): TensorNeed((B, bw), "bias"),
+                self._n("lam"): TensorNeed((C,)), self._n("o"): TensorNeed((H, C))}
+
+    def load(self, tensors, rt: Runtime) -> None:
+        w = lambda role: tensors[self._n(role)].to(device=rt.device, dtype=rt.dtype)
+        f = lambda role: tensors[self._n(role)].to(device=rt.device, dtype=torch.float32).contiguous()
+        self.xy = Linear.stacked([w("x"), w("y")])           # biases join in the kernels that read the product
+        self.o = Linear(w("o"))
+        self.x_bias, self.y_bias = f("x.b"), f("y.b")
+        self.conv_w, self.conv_b = f("conv"), f("conv.b")
+        # [blocks, out, in] -> [blocks, in, out]: the threads of a warp then read neighbouring outputs
+        self.wa_t, self.wb_t = f("ra").transpose(1, 2).contiguous(), f("ri").transpose(1, 2).contiguous()
+        self.ba, self.bb = f("ra.b").reshape(-1).contiguous(), f("ri.b").reshape(-1).contiguous()
+        # softplus of the decay parameter is a constant of the weights: folded once, in float64
+        lam = tensors[self._n("lam")].to(torch.float64)
+        self.softplus_lam = torch.nn.functional.softplus(lam).to(device=rt.device, dtype=torch.float32).contiguous()
+
+    def weight_bytes(self) -> int:
+        small = (self.x_bias, self.y_bias, self.conv_w, self.conv_b, self.wa_t, self.wb_t, self.ba, self.bb, self.softplus_lam)
+        return self.xy.weight_bytes() + self.o.weight_bytes() + sum(t.numel() * 4 for t in small)
+
+    def flops(self, num_tokens: int) -> float:
+        gates = 4.0 * num_tokens * self.width * (self.width // self.blocks)
+        return self.xy.flops(num_tokens) + self.o.flops(num_tokens) + gates
+
+    def cache_bytes_read(self, q_lens, kv_lens, itemsize: int) -> int:
+        return len(q_lens) * self.taps * self.width * 4
+
+    def forward(self, h, ctx, cache: CacheView):
+        C = self.width
+        T = h.shape[0]
+        xy = self.xy(h, out_dtype=torch.float32)
+        u = torch.empty((T, C), device=h.device, dtype=torch.float32)
+        if self.taps > 1:
+            conv = cache.parts["conv"]
+            conv_state, conv_slots = conv.state, ctx.state_slots[conv.group]
+        else:
+            conv_state, conv_slots = u, ctx.state_slots[cache.parts["state"].group]      # never read: no tap reaches back
+        ops.causal_conv(xy[:, :C], self.x_bias, self.conv_w, self.conv_b, conv_state, conv_slots, ctx.cu_q,
+                        ctx.seq_of_token, u)
+        r, g = torch.empty_like(u), torch.empty_like(u)
+        ops.block_gates(u, self.wa_t, self.ba, self.wb_t, self.bb, r, g)
+        st = cache.parts["state"]
+        mixed = torch.empty((T, C), device=h.device, dtype=h.dtype)
+        ops.gated_scan(u, r, g, xy[:, C:], self.y_bias, self.softplus_lam, -self.rate, st.state,
+                       ctx.state_slots[st.group], ctx.cu_q, ctx.num_seqs, mixed)
+        return self.o(mixed)
