@@ -233,9 +233,9 @@ def time_parts(runner, q_lens: list, kv_lens: list, reps: int = 5, layer: int = 
     ctx = runner.prepare(entries)
     entry = model.plan.schedule[layer]
     block = model.blocks[entry.layer]
-    k_pages, v_pages = runner.storage.pages(entry.cache)
-    from .parts import CacheView
-    view = CacheView(runner.manager.plan.group_of_slot[entry.cache], entry.writes, k_pages=k_pages, v_pages=v_pages)
+    view = model._cache_view(runner.storage, entry)
+    if getattr(block, "token_shift", None) is not None:      # the block keeps a row of its own beside its mixer's cache
+        view = view.parts.get("mixer")
     T = sum(q_lens)
     h = (torch.randn((T, model.plan.hidden_size), device=dev) * 0.5).to(runner.rt.dtype)
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)

@@ -12,8 +12,11 @@
 // staged in shared memory, the partial sums of the chunk reduced over the groups afterwards), and writes S back.
 #include "common.cuh"
 
+// the most threads of a block by the rows a thread keeps: the registers of the whole block have to fit an SM's file
+constexpr int ret_max_threads(int R) { return R <= 16 ? 1024 : (R <= 32 ? 512 : 256); }
+
 template <typename T, int R>
-__global__ void retention_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v, int ld,
+__global__ void __launch_bounds__(ret_max_threads(R)) retention_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v, int ld,
                                  const float* __restrict__ cos_sin, int rot, int table_rows,
                                  const int* __restrict__ positions, const float* __restrict__ decay, float k_scale,
                                  float* __restrict__ state, const int* __restrict__ slots,
@@ -155,8 +158,8 @@ ACV_API int acv_retention(const void* q, const void* k, const void* v, int ld, c
     if (num_seqs <= 0) return 0;
     if (H <= 0 || D <= 0 || DV <= 0 || DV > 1024 || (cos_sin && (rot <= 0 || rot > D || (rot & 1)))) return ACV_ERR_SIZE;
     int R = 4;
-    while (R <= 64 && ((D + R - 1) / R) * DV > 1024) R *= 2;
-    if (R > 64) return ACV_ERR_SIZE;
+    while (R <= 64 && ((D + R - 1) / R) * DV > ret_max_threads(R)) R *= 2;
+    if (R > 64) return ACV_ERR_SIZE;      // (a state of more than 64 x 256 elements per head is not built)
     if (dtype == ACV_F32)
         return retention_by_rows<float>(R, q, k, v, ld, cos_sin, rot, table_rows, positions, decay, k_scale, state, slots,
                                         cu_q, o, ldo, num_seqs, H, D, DV, stream);

@@ -201,7 +201,7 @@ class Attention(Mixer):
                                         table, kp, vp, table_rows=rows)
         out = torch.empty((qkv.shape[0], self.q_size), device=h.device, dtype=h.dtype)
         ops.attention(qkv, out, cache.k_pages, cache.v_pages, ctx, table, NH, NKV, D, self.scale, self.window,
-                      work=ctx.work[self.metadata_key], keep_first=self.keep_first)
+                      work=ctx.work[self.metadata_key], **({"keep_first": self.keep_first} if self.keep_first else {}))
         return self.o(out)
 
 

@@ -228,3 +228,11 @@ def forward(cfg, W, tokens, return_streams=False):
     if cap > 0.0:
         logits = cap * np.tanh(logits / cap)
     return (logits, streams) if return_streams else logits
+
+
+def greedy(cfg, W, prompt, n):
+    """The n tokens that follow ``prompt`` when the most probable token is always taken (the lowest id on a tie)."""
+    ids = list(prompt)
+    for _ in range(n):
+        ids.append(int(np.argmax(forward(cfg, W, ids)[-1])))
+    return ids[len(prompt):]
