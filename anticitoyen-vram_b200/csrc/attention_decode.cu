@@ -37,6 +37,7 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ 
                    int flags) {
     const int cluster_merge = flags & 1;        // the splits of a (request, kv-head) are one cluster
     const bool out_f32 = flags & 2;             // out is float (a caller that goes on computing with the result in 32-bit)
+    const int keep_first = flags >> 8;          // with a window: the first keys of the request stay visible behind it
     constexpr int CH = D / 8;                 // 16-byte chunks per row
     constexpr int AD_THREADS = NW * 32;
     constexpr int WT_BYTES = 16 * D * 2;                         // 16 keys (or values) of one kv-head
@@ -64,16 +65,20 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ 
     // the first key the query sees: the window's lower edge and/or the start of its chunk (counted from position 0)
     int lo = window > 0 ? max(0, p - window + 1) : 0;
     if (chunk_mask > 0) lo = max(lo, p / chunk_mask * chunk_mask);
-    const int n_keys = p + 1 - lo;
+    // The kept first keys that the window has passed, [0, kept), are read in front of the window's: the keys this
+    // query sees are numbered lo - kept .. p, and number x below lo stands for key x - (lo - kept).
+    const int kept = window > 0 && chunk_mask <= 0 ? min(keep_first, lo) : 0;
+    const int gap = lo - kept;
+    const int n_keys = p + 1 - gap;
     const int chunk = (((n_keys + n_splits - 1) / n_splits) + AD_TILE - 1) & ~(AD_TILE - 1);
-    const int beg = lo + split * chunk;
+    const int beg = gap + split * chunk;
     const int end = min(beg + chunk, p + 1);
     const int n_tiles = beg < end ? (end - beg + AD_TILE - 1) / AD_TILE : 0;   // > 0: this split has keys
 
     // the block-table entries of this CTA's keys, read once (a tile's copies then wait for no lookup)
     const int first_pg = page_shift >= 0 ? beg >> page_shift : beg / page_size;
     const int n_pg = n_tiles > 0 ? (page_shift >= 0 ? (end - 1) >> page_shift : (end - 1) / page_size) - first_pg + 1 : 0;
-    const bool pg_cached = n_pg <= pg_cap;
+    const bool pg_cached = n_pg <= pg_cap && kept == 0;     // (kept keys lie in pages far from the window's)
     if (pg_cached)
         for (int i = tid; i < n_pg; i += AD_THREADS) pg_s[i] = bt[first_pg + i];
     __syncthreads();
@@ -116,10 +121,11 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ 
 #pragma unroll
         for (int id = lane; id < 16 * CH; id += 32) {
             const int r = id / CH, c = id % CH;
-            const int j = j0 + r;
+            int j = j0 + r;
             bool ok = j < end;
             size_t row_off = 0;
             if (ok) {
+                if (j < lo) j -= gap;           // a kept first key
                 const int pi = page_shift >= 0 ? j >> page_shift : j / page_size;
                 const int in_pg = page_shift >= 0 ? j & (page_size - 1) : j - pi * page_size;
                 const int pg = pg_cached ? pg_s[pi - first_pg] : bt[pi];
@@ -539,7 +545,7 @@ static int launch_decode(const void* q, int q_stride, void* out, int out_stride,
     int page_shift = -1;
     for (int b = 0; b < 31; ++b)
         if ((1 << b) == page_size) page_shift = b;
-    const int out_f32_bit = cluster_merge & 2;      // travels with the merge flag to the kernel
+    const int out_f32_bit = cluster_merge & ~1;     // travels with the merge flag to the kernel, and so do the bits above it
     cluster_merge &= 1;
     if (n_splits < 2 || n_splits > 8) cluster_merge = 0;
     int pg_cap = 0, alone = 0;
@@ -574,9 +580,12 @@ ACV_API int acv_attention_decode(const void* q, int q_stride, void* out, int out
                                  const int* kv_len, const int* block_table, int bt_stride, const int* bt_rows, int NH,
                                  int NKV, int D, int page_size, int num_pages, float scale, int window, int chunk_mask, int n_splits, float* part_acc,
                                  float* part_ml, int* counters, long long scratch_floats, long long scratch_ml_floats,
-                                 long long scratch_counters, int max_kv, int cluster_merge, int out_f32, cudaStream_t stream) {
+                                 long long scratch_counters, int max_kv, int cluster_merge, int out_f32, int keep_first,
+                                 cudaStream_t stream) {
     if (n_dec <= 0) return 0;
-    cluster_merge = (cluster_merge ? 1 : 0) | (out_f32 ? 2 : 0);
+    if (keep_first < 0 || keep_first >= (1 << 22)) return ACV_ERR_SIZE;
+    // one word of flags for the kernel: merge inside clusters, float output, and the number of kept first keys
+    cluster_merge = (cluster_merge ? 1 : 0) | (out_f32 ? 2 : 0) | ((window > 0 ? keep_first : 0) << 8);
     if (NKV <= 0 || NH % NKV || NH / NKV > 16 || n_splits < 1 || n_splits > 65535 || NKV > 65535) return ACV_ERR_SIZE;
     if (((uintptr_t)q & 15) || ((size_t)q_stride * 2) % 16 || ((uintptr_t)k_pages & 15) || ((uintptr_t)v_pages & 15))
         return ACV_ERR_ALIGN;
@@ -689,7 +698,7 @@ ACV_API int acv_attention_decode_static(const void* q, int q_stride, void* out, 
     if (e != cudaSuccess) return (int)e;
     return acv_attention_decode(q, q_stride, out, out_stride, k_pages, v_pages, dec_tokens, dec_seqs, n_dec, kv_len,
                                 block_table, bt_stride, nullptr, NH, NKV, D, page_size, num_pages, scale, window, 0, n_splits,
-                                part_acc, part_ml, cnt, acc_floats, ml_floats, counters, max_kv, 0, 0, stream);
+                                part_acc, part_ml, cnt, acc_floats, ml_floats, counters, max_kv, 0, 0, 0, stream);
 }
 
 ACV_TL_EXPORT(attention_decode)

@@ -50,6 +50,7 @@ struct AttnTcParams {
     int bt_stride;
     const int* bt_rows;         // the row of block_table of each request of the batch (null: its index)
     int NH, NKV, page_size, page_shift, num_pages, window, chunk;
+    int keep_first;         // with a window: the first keys of a request stay visible to every later query
     int out_f32;            // out is float [T, out_stride floats] instead of bfloat16
     float scale;
     int* status;
@@ -131,7 +132,10 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     const int lo = first_seen(pos0);
     const int lo_last = first_seen(hi);                     // key tiles that begin before it need the mask
     const int j_first = lo & ~(AT_BN - 1);
-    const int n_tiles = (hi - j_first) / AT_BN + 1;
+    // key tiles in front of the window that hold kept first keys come first; tile t begins at key tile_j0(t)
+    const int n_sink = p.keep_first > 0 ? min(j_first / AT_BN, (p.keep_first + AT_BN - 1) / AT_BN) : 0;
+    const int n_tiles = n_sink + (hi - j_first) / AT_BN + 1;
+    auto tile_j0 = [&](int t) { return t < n_sink ? t * AT_BN : j_first + (t - n_sink) * AT_BN; };
     const int* bt = p.block_table + (size_t)(p.bt_rows ? p.bt_rows[seq] : seq) * p.bt_stride;
     pdl_wait();             // queries, and the keys and values of this step's tokens, are the projection's output
 
@@ -149,9 +153,9 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         for (int t = 0; t < n_tiles; ++t) {
             const int s = t & 1;
             // pages of this tile that hold keys some row reads; the others are skipped (their rows are masked)
-            const int j = j_first + t * AT_BN + lane * ps;
+            const int j = tile_j0(t) + lane * ps;
             int pg = -1;
-            if (lane < pages_per_tile && j <= hi && j + ps - 1 >= lo) pg = bt[j >> p.page_shift];
+            if (lane < pages_per_tile && j <= hi && (j + ps - 1 >= lo || j < p.keep_first)) pg = bt[j >> p.page_shift];
             const bool take = pg >= 0 && pg < p.num_pages;
             const uint32_t taken = __ballot_sync(0xffffffffu, take);
             const uint32_t k_dst = kv_s + s * 2 * KV_BYTES + lane * ps * 128, v_dst = k_dst + KV_BYTES;
@@ -252,14 +256,14 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
             tc_fence_after();
             TL_PHASE(0);
             const uint32_t tmem_sx = tmem_s + x * AT_HALF;
-            const int j0 = j_first + t * AT_BN + x * AT_HALF;
+            const int j0 = tile_j0(t) + x * AT_HALF;
             const bool need_mask = j0 + AT_HALF - 1 > pos0 || j0 < lo_last;
             uint32_t ra[32], rb[32];
             auto masked = [&](uint32_t (&raw)[32], int c0) {
 #pragma unroll
                 for (int c = 0; c < 32; ++c) {
                     const int j = j0 + c0 + c;
-                    const bool seen = j <= pos && j >= pos_lo;
+                    const bool seen = j <= pos && (j >= pos_lo || j < p.keep_first);
                     raw[c] = seen ? raw[c] : 0xff800000u;       // -inf
                 }
             };
@@ -388,7 +392,7 @@ ACV_API int acv_attention_tc(const void* q, int q_stride, int T, void* out, int 
                              const void* v_pages, const int* tile_seq, const int* tile_q0, int n_tiles, const int* cu_q,
                              const int* kv_len, const int* block_table, int bt_stride, const int* bt_rows, int NH, int NKV,
                              int D, int page_size, int num_pages, float scale, int window, int chunk, int out_f32, int* status,
-                             cudaStream_t stream) {
+                             int keep_first, cudaStream_t stream) {
     if (n_tiles <= 0) return 0;
     if (NKV <= 0 || NH % NKV || NH > 65535 || (D != 64 && D != 128)) return ACV_ERR_SIZE;
     if ((long long)n_tiles * NH > 0x7fffffffLL) return ACV_ERR_SIZE;
@@ -412,6 +416,7 @@ ACV_API int acv_attention_tc(const void* q, int q_stride, int T, void* out, int 
     p.out = (bf16*)out; p.out_stride = out_stride; p.tile_seq = tile_seq; p.tile_q0 = tile_q0; p.cu_q = cu_q;
     p.kv_len = kv_len; p.block_table = block_table; p.bt_stride = bt_stride; p.bt_rows = bt_rows; p.NH = NH; p.NKV = NKV;
     p.page_size = page_size; p.page_shift = page_shift; p.num_pages = num_pages; p.window = window; p.chunk = chunk; p.out_f32 = out_f32; p.scale = scale;
+    p.keep_first = window > 0 && keep_first > 0 ? keep_first : 0;
     p.status = status;
     if (D == 64) return launch_attn_tc<64>(mq, mk, mv, p, n_tiles, stream);
     return launch_attn_tc<128>(mq, mk, mv, p, n_tiles, stream);

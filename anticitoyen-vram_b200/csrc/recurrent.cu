@@ -5,12 +5,18 @@
 //
 //   acv_causal_conv     u[t][c] = cb[c] + sum_j w[c][K-1-j] * (x[t-j][c] + xb[c])          j = 0 .. K-1, float
 //   acv_block_gates     r = sigmoid(A_b u_b + a_b),  g = sigmoid(B_b u_b + b_b)            per block b of the channels, float
-//   acv_gated_scan      a = exp(c_r * r * sp[c]);  S = a S + sqrt(1 - a^2) * g * u;  out = S * gelu_tanh(y + yb)
+//                       a = exp(c_r * r * sp[c]),    b = sqrt(1 - a^2) * g * u             what the recurrence multiplies and adds
+//   acv_gated_scan      S = a S + b;  out = S * gelu_tanh(y + yb)
 //
 // sp[c] is softplus of the channel's decay parameter (folded when the weights are loaded), c_r the design's
 // constant (negative).  1 - a^2 is taken as -expm1(2 log a), which keeps its digits where a is close to 1.
 // Everything here is 32-bit; only the inputs x and y (a projection's output) and the result may have the run's
 // element type.
+//
+// The recurrence is linear in S, so a long portion is cut into segments of seg_len tokens that run side by side
+// (the step's list of (request, segment) items): a first launch leaves each segment's (product of a, state reached
+// from zero; the first segment starts from the request's state), a second one folds what lies before its segment
+// and walks it again, writing the outputs.  Steps of short portions and single tokens run the second launch alone.
 #include "common.cuh"
 
 // ----------------------------------------------------------------------------- short causal convolution per channel
@@ -79,7 +85,8 @@ ACV_API int acv_causal_conv(const void* x, int ldx, const float* xb, const float
 #define GT 16
 
 __global__ void block_gates_kernel(const float* __restrict__ u, const float* __restrict__ wa, const float* __restrict__ ba,
-                                   const float* __restrict__ wb, const float* __restrict__ bb, float* __restrict__ r,
+                                   const float* __restrict__ wb, const float* __restrict__ bb,
+                                   const float* __restrict__ sp, float c_r, float* __restrict__ r,
                                    float* __restrict__ g, int T, int C, int BW) {
     extern __shared__ float su[];          // [GT][BW]
     pdl_launch_dependents();
@@ -108,18 +115,23 @@ __global__ void block_gates_kernel(const float* __restrict__ u, const float* __r
         }
         const int ch = blk * BW + o;
         const float b1 = ba ? ba[ch] : 0.f, b2 = bb ? bb[ch] : 0.f;
+        const float rate = c_r * sp[ch];
 #pragma unroll
         for (int tt = 0; tt < GT; ++tt) {
             if (tt < nt) {
-                r[(size_t)(t0 + tt) * C + ch] = 1.f / (1.f + expf(-(ar[tt] + b1)));
-                g[(size_t)(t0 + tt) * C + ch] = 1.f / (1.f + expf(-(ag[tt] + b2)));
+                const float rr = 1.f / (1.f + expf(-(ar[tt] + b1)));
+                const float gg = 1.f / (1.f + expf(-(ag[tt] + b2)));
+                const float la = rate * rr;                    // log a <= 0
+                r[(size_t)(t0 + tt) * C + ch] = expf(la);
+                g[(size_t)(t0 + tt) * C + ch] = sqrtf(fmaxf(-expm1f(2.f * la), 0.f)) * gg * su[tt * BW + o];
             }
         }
     }
 }
 
-ACV_API int acv_block_gates(const float* u, const float* wa, const float* ba, const float* wb, const float* bb, float* r,
-                            float* g, int T, int C, int blocks, cudaStream_t stream) {
+// r <- a, g <- b of the recurrence (see the head of the file)
+ACV_API int acv_block_gates(const float* u, const float* wa, const float* ba, const float* wb, const float* bb,
+                            const float* sp, float c_r, float* r, float* g, int T, int C, int blocks, cudaStream_t stream) {
     if (T <= 0) return 0;
     if (blocks <= 0 || C % blocks) return ACV_ERR_SIZE;
     const int BW = C / blocks;
@@ -132,7 +144,7 @@ ACV_API int acv_block_gates(const float* u, const float* wa, const float* ba, co
     }
     dim3 grid((T + GT - 1) / GT, blocks);
     const int threads = BW >= 256 ? 256 : (BW >= 128 ? 128 : (BW > 32 ? 64 : 32));
-    acv_launch(PDL_MISC, block_gates_kernel, grid, threads, smem, stream, u, wa, ba, wb, bb, r, g, T, C, BW);
+    acv_launch(PDL_MISC, block_gates_kernel, grid, threads, smem, stream, u, wa, ba, wb, bb, sp, c_r, r, g, T, C, BW);
     return acv_launch_status();
 }
 
@@ -141,68 +153,101 @@ __device__ __forceinline__ float gelu_tanh_f32(float z) {
     return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
 }
 
-// grid (requests, channel tiles): a thread walks its channel through the request's tokens of this step; the loads of
-// SC tokens are issued before their recurrence runs, so that they do not wait for one another.
+// grid (items, channel tiles): a thread walks its channel through the item's tokens; the loads of SC tokens are issued
+// before their recurrence runs, so that they do not wait for one another.  An item is a segment of a request's portion:
+// tokens cu_q[seq] + z * seg_len .. (seg_len of them, or what is left).
 #define SC 8
 
-template <typename TY, typename T>
-__global__ void gated_scan_kernel(const float* __restrict__ u, const float* __restrict__ r, const float* __restrict__ g,
-                                  const TY* __restrict__ y, int ldy, const float* __restrict__ yb,
-                                  const float* __restrict__ sp, float c_r, float* __restrict__ state,
-                                  const int* __restrict__ slots, const int* __restrict__ cu_q, T* __restrict__ out,
-                                  int ldo, int C) {
+// what lies in front of segment z of a request whose first segment is item `first`: the fold of the segments' (A, B)
+__device__ __forceinline__ float fold_segments(const float* __restrict__ seg, int first, int z, int C, int c) {
+    float S = seg[((size_t)first * 2 + 1) * C + c];            // the first segment began at the request's state
+    for (int zz = 1; zz < z; ++zz) {
+        const float* e = seg + (size_t)(first + zz) * 2 * C;
+        S = fmaf(e[c], S, e[C + c]);
+    }
+    return S;
+}
+
+// SUMMARY: leave (A, B) of the segment in seg[item] and write no output (the last segment of a request does nothing)
+template <typename TY, typename T, bool SUMMARY>
+__global__ void gated_scan_kernel(const float* __restrict__ a, const float* __restrict__ b, const TY* __restrict__ y, int ldy,
+                                  const float* __restrict__ yb, float* __restrict__ state, const int* __restrict__ slots,
+                                  const int* __restrict__ cu_q, const int* __restrict__ seg_seq,
+                                  const int* __restrict__ seg_idx, int seg_len, float* __restrict__ seg,
+                                  T* __restrict__ out, int ldo, int C) {
     pdl_launch_dependents();
     pdl_wait();
-    const int seq = blockIdx.x;
+    const int item = blockIdx.x;
     const int c = blockIdx.y * blockDim.x + threadIdx.x;
     if (c >= C) return;
-    const int t0 = cu_q[seq], t1 = cu_q[seq + 1];
+    const int seq = seg_seq ? seg_seq[item] : item, z = seg_idx ? seg_idx[item] : 0;
+    const int q0 = cu_q[seq], q1 = cu_q[seq + 1];
+    const int t0 = q0 + z * seg_len, t1 = min(q1, t0 + seg_len);
     if (t1 <= t0) return;
+    const bool last = t1 == q1;
+    if (SUMMARY && last) return;
     float* st = state + (size_t)slots[seq] * C + c;
-    float S = *st;
-    const float rate = c_r * sp[c];
+    // The request's state as this step found it: read from its slot by the first launch (and by a request's only
+    // segment), which also leaves it in the unused entry of the request's last segment for the second launch, whose
+    // last segment replaces the slot while its first one may not have begun.
+    const int last_item = item - z + (q1 - q0 + seg_len - 1) / seg_len - 1;
+    float S;
+    if (z == 0) {
+        S = (SUMMARY || last) ? *st : seg[((size_t)last_item * 2) * C + c];
+        if (SUMMARY) seg[((size_t)last_item * 2) * C + c] = S;
+    } else {
+        S = SUMMARY ? 0.f : fold_segments(seg, item - z, z, C, c);
+    }
+    float A = 1.f;
     const float bias_y = yb ? yb[c] : 0.f;
     for (int t = t0; t < t1; t += SC) {
-        float uu[SC], rr[SC], gg[SC], yy[SC];
+        float aa[SC], bb[SC], yy[SC];
 #pragma unroll
         for (int i = 0; i < SC; ++i) {
             const bool in = t + i < t1;
             const size_t at = (size_t)(in ? t + i : t) * C + c;
-            uu[i] = u[at];
-            rr[i] = r[at];
-            gg[i] = g[at];
-            yy[i] = to_f32(y[(size_t)(in ? t + i : t) * ldy + c]);
+            aa[i] = a[at];
+            bb[i] = b[at];
+            if (!SUMMARY) yy[i] = gelu_tanh_f32(to_f32(y[(size_t)(in ? t + i : t) * ldy + c]) + bias_y);
         }
 #pragma unroll
         for (int i = 0; i < SC; ++i) {
             if (t + i < t1) {
-                const float la = rate * rr[i];                 // log a <= 0
-                const float a = expf(la);
-                const float m = sqrtf(fmaxf(-expm1f(2.f * la), 0.f));
-                S = fmaf(a, S, m * gg[i] * uu[i]);
-                out[(size_t)(t + i) * ldo + c] = from_f32<T>(S * gelu_tanh_f32(yy[i] + bias_y));
+                S = fmaf(aa[i], S, bb[i]);
+                if (SUMMARY) A *= aa[i];
+                else out[(size_t)(t + i) * ldo + c] = from_f32<T>(S * yy[i]);
             }
         }
     }
-    *st = S;
+    if (SUMMARY) {
+        seg[((size_t)item * 2) * C + c] = A;
+        seg[((size_t)item * 2 + 1) * C + c] = S;
+    } else if (last) {
+        *st = S;
+    }
 }
 
-ACV_API int acv_gated_scan(const float* u, const float* r, const float* g, const void* y, int ldy, const float* yb,
-                           const float* sp, float c_r, float* state, const int* slots, const int* cu_q, void* out, int ldo,
-                           int num_seqs, int C, int y_dtype, int dtype, cudaStream_t stream) {
-    if (num_seqs <= 0) return 0;
-    if (C <= 0) return ACV_ERR_SIZE;
-    dim3 grid(num_seqs, (C + 63) / 64);
-    if (y_dtype == ACV_F32 && dtype == ACV_F32)
-        acv_launch(PDL_MISC, gated_scan_kernel<float, float>, grid, 64, 0, stream, u, r, g, (const float*)y, ldy, yb, sp, c_r,
-                   state, slots, cu_q, (float*)out, ldo, C);
-    else if (y_dtype == ACV_F32 && dtype == ACV_BF16)
-        acv_launch(PDL_MISC, gated_scan_kernel<float, bf16>, grid, 64, 0, stream, u, r, g, (const float*)y, ldy, yb, sp, c_r,
-                   state, slots, cu_q, (bf16*)out, ldo, C);
-    else if (y_dtype == ACV_BF16 && dtype == ACV_BF16)
-        acv_launch(PDL_MISC, gated_scan_kernel<bf16, bf16>, grid, 64, 0, stream, u, r, g, (const bf16*)y, ldy, yb, sp, c_r,
-                   state, slots, cu_q, (bf16*)out, ldo, C);
-    else
-        return ACV_ERR_DTYPE;
-    return acv_launch_status();
+// a, b: float [T, C] (acv_block_gates); seg_seq, seg_idx: the step's items (null: one item for each request, its whole
+// portion); seg: float [items][2][C] scratch of the first launch, which runs when `summaries` is set.
+ACV_API int acv_gated_scan(const float* a, const float* b, const void* y, int ldy, const float* yb, float* state,
+                           const int* slots, const int* cu_q, const int* seg_seq, const int* seg_idx, int seg_len,
+                           float* seg, int summaries, void* out, int ldo, int n_items, int C, int y_dtype, int dtype,
+                           cudaStream_t stream) {
+    if (n_items <= 0) return 0;
+    if (C <= 0 || seg_len <= 0 || (summaries && (!seg || !seg_seq || !seg_idx))) return ACV_ERR_SIZE;
+    dim3 grid(n_items, (C + 63) / 64);
+#define SCAN_LAUNCH(TY, T)                                                                                           \
+    {                                                                                                                \
+        if (summaries)                                                                                               \
+            acv_launch(PDL_MISC, gated_scan_kernel<TY, T, true>, grid, 64, 0, stream, a, b, (const TY*)y, ldy, yb, state, \
+                       slots, cu_q, seg_seq, seg_idx, seg_len, seg, (T*)out, ldo, C);                               \
+        acv_launch(PDL_MISC, gated_scan_kernel<TY, T, false>, grid, 64, 0, stream, a, b, (const TY*)y, ldy, yb, state,    \
+                   slots, cu_q, seg_seq, seg_idx, seg_len, seg, (T*)out, ldo, C);                                   \
+        return acv_launch_status();                                                                                  \
+    }
+    if (y_dtype == ACV_F32 && dtype == ACV_F32) SCAN_LAUNCH(float, float)
+    if (y_dtype == ACV_F32 && dtype == ACV_BF16) SCAN_LAUNCH(float, bf16)
+    if (y_dtype == ACV_BF16 && dtype == ACV_BF16) SCAN_LAUNCH(bf16, bf16)
+#undef SCAN_LAUNCH
+    return ACV_ERR_DTYPE;
 }

@@ -7,20 +7,33 @@
 // multiplied by k_scale, all in float, as they are staged; scores, state and sums are 32-bit.  A second kernel
 // brings each head's o to unit RMS (no weight), multiplies by silu(gate) and a constant, and rounds once.
 //
-// acv_retention: grid (requests, heads).  The block's threads are G groups of DV: thread (g, c) keeps rows
-// g*R .. g*R+R-1 of column c of S in registers, walks the request's tokens of this step in chunks of TC (q, k, v
-// staged in shared memory, the partial sums of the chunk reduced over the groups afterwards), and writes S back.
+// acv_retention: grid (items, heads).  The block's threads are G groups of DV: thread (g, c) keeps rows
+// g*R .. g*R+R-1 of column c of S in registers, walks its tokens in chunks of TC (q, k, v staged in shared memory,
+// the partial sums of the chunk reduced over the groups afterwards), and writes S back.
+//
+// The recurrence is linear in S, so a long portion is cut into segments of seg_len tokens that run side by side (the
+// step's list of (request, segment) items): a first launch leaves the state that each segment reaches from zero (the
+// first one from the request's state), without outputs; a second one folds what lies before its segment,
+// S_in(z) = decay^seg_len S_in(z-1) + S_seg(z-1), and walks the segment again with outputs.  Steps of short portions and
+// single tokens run the second launch alone.
 #include "common.cuh"
 
 // the most threads of a block by the rows a thread keeps: the registers of the whole block have to fit an SM's file
 constexpr int ret_max_threads(int R) { return R <= 16 ? 1024 : (R <= 32 ? 512 : 256); }
 
-template <typename T, int R>
+struct RetSegments {
+    const int* seq;         // the request of each item (null: item i is request i, whole)
+    const int* idx;         // its segment's number
+    int len;                // tokens of a segment
+    float* state;           // [items][H][D][DV]: what the first launch leaves
+};
+
+template <typename T, int R, bool SUMMARY>
 __global__ void __launch_bounds__(ret_max_threads(R)) retention_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v, int ld,
                                  const float* __restrict__ cos_sin, int rot, int table_rows,
                                  const int* __restrict__ positions, const float* __restrict__ decay, float k_scale,
                                  float* __restrict__ state, const int* __restrict__ slots,
-                                 const int* __restrict__ cu_q, float* __restrict__ o, int ldo, int H, int D, int DV,
+                                 const int* __restrict__ cu_q, RetSegments sg, float* __restrict__ o, int ldo, int H, int D, int DV,
                                  int G, int TC) {
     extern __shared__ float sm[];
     float* qs = sm;                         // [TC][D]
@@ -29,19 +42,43 @@ __global__ void __launch_bounds__(ret_max_threads(R)) retention_kernel(const T* 
     float* red = vs + (size_t)TC * DV;      // [TC][G][DV]
     pdl_launch_dependents();
     pdl_wait();
-    const int seq = blockIdx.x, h = blockIdx.y;
-    const int t0 = cu_q[seq], t1 = cu_q[seq + 1];
+    const int item = blockIdx.x, h = blockIdx.y;
+    const int seq = sg.seq ? sg.seq[item] : item, z = sg.idx ? sg.idx[item] : 0;
+    const int q0 = cu_q[seq], q1 = cu_q[seq + 1];
+    const int t0 = q0 + z * sg.len, t1 = min(q1, t0 + sg.len);
     if (t1 <= t0) return;
+    const bool last = t1 == q1;
+    if (SUMMARY && last) return;
     const int tid = threadIdx.x, nthr = blockDim.x;
     const int c = tid % DV, g = tid / DV;
     const bool owner = g < G;
     const float dec = decay[h];
-    float* st = state + ((size_t)slots[seq] * H + h) * D * DV;
+    const size_t HS = (size_t)D * DV;
+    float* st = state + ((size_t)slots[seq] * H + h) * HS;
+    // The request's state as this step found it: read from its slot by the first launch (and by a request's only
+    // segment), which also leaves it in the unused entry of the request's last segment for the second launch, whose
+    // last segment replaces the slot while its first one may not have begun.
+    const int last_item = item - z + (q1 - q0 + sg.len - 1) / sg.len - 1;
+    float* keep = sg.state ? sg.state + ((size_t)last_item * H + h) * HS : nullptr;
     float S[R];
 #pragma unroll
     for (int i = 0; i < R; ++i) {
         const int d = g * R + i;
-        S[i] = owner && d < D ? st[(size_t)d * DV + c] : 0.f;
+        float s0 = 0.f;
+        if (owner && d < D) {
+            const size_t at = (size_t)d * DV + c;
+            if (z == 0) {
+                s0 = (SUMMARY || last) ? st[at] : keep[at];
+                if (SUMMARY) keep[at] = s0;
+            } else if (!SUMMARY) {
+                // what lies in front of this segment: the first segment began at the request's state
+                const float* e = sg.state + ((size_t)(item - z) * H + h) * HS + at;
+                s0 = *e;
+                const float dec_len = exp2f((float)sg.len * log2f(dec));
+                for (int zz = 1; zz < z; ++zz) s0 = fmaf(dec_len, s0, e[(size_t)zz * H * HS]);
+            }
+        }
+        S[i] = s0;
     }
     const int half = rot >> 1;
     for (int tb = t0; tb < t1; tb += TC) {
@@ -85,27 +122,30 @@ __global__ void __launch_bounds__(ret_max_threads(R)) retention_kernel(const T* 
                 for (int i = 0; i < R; ++i) {
                     if (g * R + i < D) {
                         S[i] = fmaf(dec, S[i], kr[i] * vv);
-                        part = fmaf(S[i], qr[i], part);
+                        if (!SUMMARY) part = fmaf(S[i], qr[i], part);
                     }
                 }
-                red[((size_t)tt * G + g) * DV + c] = part;
+                if (!SUMMARY) red[((size_t)tt * G + g) * DV + c] = part;
             }
         }
         __syncthreads();
-        for (int i = tid; i < n * DV; i += nthr) {
-            const int tt = i / DV, e = i - tt * DV;
-            float sum = 0.f;
-            for (int gg = 0; gg < G; ++gg) sum += red[((size_t)tt * G + gg) * DV + e];
-            o[(size_t)(tb + tt) * ldo + (size_t)h * DV + e] = sum;
+        if (!SUMMARY) {
+            for (int i = tid; i < n * DV; i += nthr) {
+                const int tt = i / DV, e = i - tt * DV;
+                float sum = 0.f;
+                for (int gg = 0; gg < G; ++gg) sum += red[((size_t)tt * G + gg) * DV + e];
+                o[(size_t)(tb + tt) * ldo + (size_t)h * DV + e] = sum;
+            }
         }
         // the next chunk's staging writes qs, ks, vs only; its first barrier stands between this read of red and the
         // next write of it
     }
-    if (owner) {
+    if (owner && (SUMMARY || last)) {
+        float* dst = SUMMARY ? sg.state + ((size_t)item * H + h) * HS : st;
 #pragma unroll
         for (int i = 0; i < R; ++i) {
             const int d = g * R + i;
-            if (d < D) st[(size_t)d * DV + c] = S[i];
+            if (d < D) dst[(size_t)d * DV + c] = S[i];
         }
     }
 }
@@ -113,7 +153,7 @@ __global__ void __launch_bounds__(ret_max_threads(R)) retention_kernel(const T* 
 template <typename T, int R>
 static int launch_retention(const void* q, const void* k, const void* v, int ld, const float* cos_sin, int rot,
                             int table_rows, const int* positions, const float* decay, float k_scale, float* state,
-                            const int* slots, const int* cu_q, float* o, int ldo, int num_seqs, int H, int D, int DV,
+                            const int* slots, const int* cu_q, RetSegments sg, int summaries, float* o, int ldo, int num_seqs, int H, int D, int DV,
                             cudaStream_t stream) {
     const int G = (D + R - 1) / R;
     const int threads = ((G * DV + 31) / 32) * 32;
@@ -124,24 +164,28 @@ static int launch_retention(const void* q, const void* k, const void* v, int ld,
     const size_t smem = per_token * TC;
     if (smem > 200 * 1024) return ACV_ERR_SIZE;
     if (smem > 48 * 1024) {
-        static AcvSmemConfig cfg;
-        const int e = acv_ensure_smem(cfg, retention_kernel<T, R>, (int)smem);
+        static AcvSmemConfig cfg, cfg_s;
+        int e = acv_ensure_smem(cfg, retention_kernel<T, R, false>, (int)smem);
+        if (!e && summaries) e = acv_ensure_smem(cfg_s, retention_kernel<T, R, true>, (int)smem);
         if (e) return e;
     }
-    acv_launch(PDL_ATTN, retention_kernel<T, R>, dim3(num_seqs, H), threads, smem, stream, (const T*)q, (const T*)k,
-               (const T*)v, ld, cos_sin, rot, table_rows, positions, decay, k_scale, state, slots, cu_q, o, ldo, H, D, DV, G, TC);
+    if (summaries)
+        acv_launch(PDL_ATTN, retention_kernel<T, R, true>, dim3(num_seqs, H), threads, smem, stream, (const T*)q, (const T*)k,
+                   (const T*)v, ld, cos_sin, rot, table_rows, positions, decay, k_scale, state, slots, cu_q, sg, o, ldo, H, D, DV, G, TC);
+    acv_launch(PDL_ATTN, retention_kernel<T, R, false>, dim3(num_seqs, H), threads, smem, stream, (const T*)q, (const T*)k,
+               (const T*)v, ld, cos_sin, rot, table_rows, positions, decay, k_scale, state, slots, cu_q, sg, o, ldo, H, D, DV, G, TC);
     return acv_launch_status();
 }
 
 template <typename T>
 static int retention_by_rows(int R, const void* q, const void* k, const void* v, int ld, const float* cos_sin, int rot,
                              int table_rows, const int* positions, const float* decay, float k_scale, float* state,
-                             const int* slots, const int* cu_q, float* o, int ldo, int num_seqs, int H, int D, int DV,
+                             const int* slots, const int* cu_q, RetSegments sg, int summaries, float* o, int ldo, int num_seqs, int H, int D, int DV,
                              cudaStream_t stream) {
 #define RET_CASE(N)                                                                                                  \
     case N:                                                                                                          \
         return launch_retention<T, N>(q, k, v, ld, cos_sin, rot, table_rows, positions, decay, k_scale, state, slots, \
-                                      cu_q, o, ldo, num_seqs, H, D, DV, stream);
+                                      cu_q, sg, summaries, o, ldo, num_seqs, H, D, DV, stream);
     switch (R) {
         RET_CASE(4) RET_CASE(8) RET_CASE(16) RET_CASE(32) RET_CASE(64)
     }
@@ -151,21 +195,28 @@ static int retention_by_rows(int R, const void* q, const void* k, const void* v,
 
 // q, k: rows of H*D at stride ld; v: rows of H*DV at stride ld; o: float rows of H*DV at stride ldo;
 // state: [slots][H][D][DV] float; decay: [H] float; cos_sin: [table_rows][rot] float or null.
+// seg_seq, seg_idx: the step's n_items items (null: one item for each request, its whole portion); seg_state: float
+// [n_items][H][D][DV] scratch of the first launch, which runs when `summaries` is set.
 ACV_API int acv_retention(const void* q, const void* k, const void* v, int ld, const float* cos_sin, int rot,
                           int table_rows, const int* positions, const float* decay, float k_scale, float* state,
-                          const int* slots, const int* cu_q, float* o, int ldo, int num_seqs, int H, int D, int DV,
+                          const int* slots, const int* cu_q, const int* seg_seq, const int* seg_idx, int seg_len,
+                          float* seg_state, int summaries, float* o, int ldo, int n_items, int H, int D, int DV,
                           int dtype, cudaStream_t stream) {
+    const int num_seqs = n_items;
     if (num_seqs <= 0) return 0;
     if (H <= 0 || D <= 0 || DV <= 0 || DV > 1024 || (cos_sin && (rot <= 0 || rot > D || (rot & 1)))) return ACV_ERR_SIZE;
+    if (seg_len <= 0 || (summaries && (!seg_seq || !seg_idx || !seg_state))) return ACV_ERR_SIZE;
+    RetSegments sg;
+    sg.seq = seg_seq; sg.idx = seg_idx; sg.len = seg_len; sg.state = seg_state;
     int R = 4;
     while (R <= 64 && ((D + R - 1) / R) * DV > ret_max_threads(R)) R *= 2;
     if (R > 64) return ACV_ERR_SIZE;      // (a state of more than 64 x 256 elements per head is not built)
     if (dtype == ACV_F32)
         return retention_by_rows<float>(R, q, k, v, ld, cos_sin, rot, table_rows, positions, decay, k_scale, state, slots,
-                                        cu_q, o, ldo, num_seqs, H, D, DV, stream);
+                                        cu_q, sg, summaries, o, ldo, num_seqs, H, D, DV, stream);
     if (dtype == ACV_BF16)
         return retention_by_rows<bf16>(R, q, k, v, ld, cos_sin, rot, table_rows, positions, decay, k_scale, state, slots,
-                                       cu_q, o, ldo, num_seqs, H, D, DV, stream);
+                                       cu_q, sg, summaries, o, ldo, num_seqs, H, D, DV, stream);
     return ACV_ERR_DTYPE;
 }
 

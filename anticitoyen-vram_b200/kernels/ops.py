@@ -77,15 +77,15 @@ def _declare(lib: ctypes.CDLL) -> None:
         "acv_add_row_f32": [P, P, I, I, P],
         "acv_softcap_f32": [P, LL, F, P],
         "acv_causal_conv": [P, I, P, P, P, P, P, P, P, P, I, I, I, I, P],
-        "acv_block_gates": [P, P, P, P, P, P, P, I, I, I, P],
-        "acv_gated_scan": [P, P, P, P, I, P, P, F, P, P, P, P, I, I, I, I, I, P],
-        "acv_retention": [P, P, P, I, P, I, I, P, P, F, P, P, P, P, I, I, I, I, I, I, P],
+        "acv_block_gates": [P, P, P, P, P, P, F, P, P, I, I, I, P],
+        "acv_gated_scan": [P, P, P, I, P, P, P, P, P, P, I, P, I, P, I, I, I, I, I, P],
+        "acv_retention": [P, P, P, I, P, I, I, P, P, F, P, P, P, P, P, I, P, I, P, I, I, I, I, I, I, P],
         "acv_retention_gate": [P, I, P, I, P, I, I, I, I, F, F, I, P],
         "acv_gemm_simt": [P, I, P, I, P, I, I, I, I, I, I, P],
         "acv_gemm_tc_qkv": [P, I, P, I, P, I, I, I, I, I, I, I, P, LL, P, LL, P, I, I, I, I, I, I, P, P, F, P, I, P, P, P, I, P, P, P, I, I, P],
         "acv_gemm_tc": [P, I, P, I, P, I, I, I, I, I, I, I, I, I, P, LL, P, LL, P, I, I, I, P],
-        "acv_attention_decode": [P, I, P, I, P, P, P, P, I, P, P, I, P, I, I, I, I, I, F, I, I, I, P, P, P, LL, LL, LL, I, I, I, P],
-        "acv_attention_tc": [P, I, I, P, I, P, P, P, P, I, P, P, P, I, P, I, I, I, I, I, F, I, I, I, P, P],
+        "acv_attention_decode": [P, I, P, I, P, P, P, P, I, P, P, I, P, I, I, I, I, I, F, I, I, I, P, P, P, LL, LL, LL, I, I, I, I, P],
+        "acv_attention_tc": [P, I, I, P, I, P, P, P, P, I, P, P, P, I, P, I, I, I, I, I, F, I, I, I, P, I, P],
         "acv_attention_chunk": [P, I, P, I, P, P, P, P, I, P, P, P, I, P, I, I, I, I, I, F, I, I, I, I, P],
         "acv_table_update": [P, I, I, P, I, P],
         "acv_embed_scaled": [P, P, P, I, I, I, F, I, P],
@@ -707,7 +707,7 @@ def attention_decode(q: torch.Tensor, out: torch.Tensor, k_pages: torch.Tensor, 
                      dec_tokens: torch.Tensor, dec_seqs: torch.Tensor, n_dec: int, kv_len: torch.Tensor,
                      block_table: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int, scale: float,
                      window: int, n_splits: int, max_kv: int = 0, cluster_merge: bool = True,
-                     table_rows: torch.Tensor | None = None, chunk: int = 0) -> torch.Tensor:
+                     table_rows: torch.Tensor | None = None, chunk: int = 0, keep_first: int = 0) -> torch.Tensor:
     """Attention of requests that bring one token each, over their pages, split over the context.
 
     Up to 8 splits are merged inside a thread-block cluster (through its shared memory); more, or
@@ -721,7 +721,7 @@ def attention_decode(q: torch.Tensor, out: torch.Tensor, k_pages: torch.Tensor, 
         _p(kv_len), _p(block_table), block_table.stride(0), _p(table_rows), num_heads, num_kv_heads, head_dim,
         k_pages.shape[2], k_pages.shape[0], scale, window, chunk, n_splits, _p(acc), _p(ml), _p(cnt), acc.numel(), ml.numel(), cnt.numel(),
         max_kv or block_table.shape[1] * k_pages.shape[2], 1 if use_cluster else 0,
-        1 if out.dtype == torch.float32 else 0, _stream()), "attention_decode")
+        1 if out.dtype == torch.float32 else 0, int(keep_first), _stream()), "attention_decode")
     return out
 
 
@@ -742,14 +742,14 @@ def attention_chunk(q: torch.Tensor, out: torch.Tensor, k_pages: torch.Tensor, v
 def attention_tc(q: torch.Tensor, out: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
                  tile_seq: torch.Tensor, tile_q0: torch.Tensor, n_tiles: int, cu_q: torch.Tensor, kv_len: torch.Tensor,
                  block_table: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int, scale: float,
-                 window: int, table_rows: torch.Tensor | None = None, chunk: int = 0) -> torch.Tensor:
+                 window: int, table_rows: torch.Tensor | None = None, chunk: int = 0, keep_first: int = 0) -> torch.Tensor:
     """Causal attention of portions of prompts on tcgen05 (tiles of QUERY_TILE query tokens, pages by TMA)."""
     _, _, status = _gemm_buffers(q.device, 0, 0)
     _check(library().acv_attention_tc(
         _p(q), q.stride(0), q.shape[0], _p(out), out.stride(0), _p(k_pages), _p(v_pages), _p(tile_seq), _p(tile_q0),
         n_tiles, _p(cu_q), _p(kv_len), _p(block_table), block_table.stride(0), _p(table_rows), num_heads, num_kv_heads,
         head_dim, k_pages.shape[2], k_pages.shape[0], scale, window, chunk, 1 if out.dtype == torch.float32 else 0, _p(status),
-        _stream()), "attention_tc")
+        int(keep_first), _stream()), "attention_tc")
     return out
 
 
@@ -821,24 +821,29 @@ def attention(qkv: torch.Tensor, out: torch.Tensor, k_pages: torch.Tensor, v_pag
     rows = getattr(ctx, "table_rows", None)
     value_dim = value_dim or head_dim
     keep_first = keep_first if window > 0 else 0
-    if value_dim != head_dim or keep_first > 0 or not tensor_core_attention_takes(qkv.dtype, num_heads, num_kv_heads, head_dim):
+    w = work if work is not None else ctx.work
+    generic = value_dim != head_dim or not tensor_core_attention_takes(qkv.dtype, num_heads, num_kv_heads, head_dim)
+    # kept first keys: the split-KV decode kernel and the tcgen05 portion kernel know them, the mma.sync portion kernel does not
+    if not generic and keep_first > 0 and (chunk > 0 or (w["n_tiles"] and not attention_tc_takes(qkv, out, k_pages, head_dim))):
+        generic = True
+    if generic:
         if chunk > 0:
             raise KernelError("attention: the chunked mask is built for the tensor-core kernels' sizes only")
         return attention_generic(qkv, out, k_pages, v_pages, ctx.positions, ctx.seq_of_token, block_table, num_heads,
                                  num_kv_heads, head_dim, scale, window, table_rows=rows, value_dim=value_dim,
                                  keep_first=keep_first)
-    w = work if work is not None else ctx.work
     if w["n_dec"]:
-        kv = min(w["max_dec_kv"], window) if window > 0 else w["max_dec_kv"]
+        kv = min(w["max_dec_kv"], window + keep_first) if window > 0 else w["max_dec_kv"]
         kv = min(kv, chunk) if chunk > 0 else kv
         n_splits, in_clusters = (w["n_splits"], True) if w.get("n_splits") else \
             decode_plan(w["n_dec"], num_heads, num_kv_heads, head_dim, k_pages.shape[2], kv)
         attention_decode(qkv, out, k_pages, v_pages, w["dec_tokens"], w["dec_seqs"], w["n_dec"], ctx.kv_len,
                          block_table, num_heads, num_kv_heads, head_dim, scale, window, n_splits, w["max_dec_kv"],
-                         cluster_merge=in_clusters, table_rows=rows, chunk=chunk)
+                         cluster_merge=in_clusters, table_rows=rows, chunk=chunk, keep_first=keep_first)
     if w["n_tiles"] and attention_tc_takes(qkv, out, k_pages, head_dim):
         attention_tc(qkv, out, k_pages, v_pages, w["tile_seq"], w["tile_q0"], w["n_tiles"], ctx.cu_q, ctx.kv_len,
-                     block_table, num_heads, num_kv_heads, head_dim, scale, window, table_rows=rows, chunk=chunk)
+                     block_table, num_heads, num_kv_heads, head_dim, scale, window, table_rows=rows, chunk=chunk,
+                     keep_first=keep_first)
     elif w["n_tiles"]:
         attention_chunk(qkv, out, k_pages, v_pages, w["tile_seq"], w["tile_q0"], w["n_tiles"], ctx.cu_q, ctx.kv_len,
                         block_table, num_heads, num_kv_heads, head_dim, scale, window, table_rows=rows,
@@ -1303,41 +1308,75 @@ def causal_conv(x: torch.Tensor, x_bias: torch.Tensor | None, taps: torch.Tensor
     return out
 
 
+SEGMENT_TOKENS = 128    # tokens of a segment of a long portion in the kernels of the linear recurrences
+
+
+def segment_work(q_lens, seg_len: int = SEGMENT_TOKENS) -> tuple[dict, dict]:
+    """The items of the recurrence kernels for a step: a request that brings more than ``seg_len`` tokens is cut into
+    segments of ``seg_len`` that run side by side (the recurrences are linear in their state: a first launch leaves
+    what each segment adds, a second one folds what lies before it).  Returns (int32 arrays that the kernels read on the
+    device: the request and the segment number of every item; counts for the launches)."""
+    import numpy as np
+    n = [max(1, -(-int(q) // seg_len)) for q in q_lens]
+    seq = np.repeat(np.arange(len(q_lens), dtype=np.int32), n)
+    idx = np.concatenate([np.arange(k, dtype=np.int32) for k in n]) if n else np.zeros(0, np.int32)
+    return ({"seg_seq": seq, "seg_idx": idx}, {"n_items": int(seq.size), "seg_len": seg_len, "summaries": max(n, default=1) > 1})
+
+
+def segment_work_decode(padded: int, seg_len: int = SEGMENT_TOKENS) -> tuple[dict, dict]:
+    """The same for a batch of ``padded`` requests with one token each."""
+    import numpy as np
+    return ({"seg_seq": np.arange(padded, dtype=np.int32), "seg_idx": np.zeros(padded, np.int32)},
+            {"n_items": padded, "seg_len": seg_len, "summaries": False})
+
+
+def _segments(work: dict | None, num_seqs: int):
+    """(seg_seq, seg_idx, seg_len, n_items, summaries) of a step's work, or one whole item for each request."""
+    if work is None:
+        return None, None, 1 << 30, num_seqs, False
+    return work["seg_seq"], work["seg_idx"], work["seg_len"], work["n_items"], work["summaries"]
+
+
 def block_gates(u: torch.Tensor, wa_t: torch.Tensor, ba: torch.Tensor | None, wb_t: torch.Tensor, bb: torch.Tensor | None,
-                r: torch.Tensor, g: torch.Tensor) -> None:
-    """r = sigmoid(A_b u_b + ba), g = sigmoid(B_b u_b + bb) per block b of the channels; wa_t, wb_t float32
-    [blocks, in, out]; u, r, g float32 [T, C]."""
-    _need_cuda(u, wa_t, wb_t, r, g)
+                softplus_rate: torch.Tensor, c_r: float, a: torch.Tensor, b: torch.Tensor) -> None:
+    """What the gated recurrence multiplies and adds at every token: r = sigmoid(A_b u_b + ba), g = sigmoid(B_b u_b + bb)
+    per block b of the channels, then a = exp(c_r * r * softplus_rate) and b = sqrt(1 - a^2) * g * u.  wa_t, wb_t float32
+    [blocks, in, out]; u, a, b float32 [T, C]."""
+    _need_cuda(u, wa_t, wb_t, a, b)
     T, C = u.shape
-    if any(t.dtype != torch.float32 or not t.is_contiguous() for t in (u, wa_t, wb_t, r, g)):
+    if any(t.dtype != torch.float32 or not t.is_contiguous() for t in (u, wa_t, wb_t, a, b, softplus_rate)):
         raise KernelError("block_gates: contiguous float32 tensors are wanted")
-    _check(library().acv_block_gates(_p(u), _p(wa_t), _p(ba), _p(wb_t), _p(bb), _p(r), _p(g), T, C, wa_t.shape[0], _stream()),
-           "block_gates")
+    _check(library().acv_block_gates(_p(u), _p(wa_t), _p(ba), _p(wb_t), _p(bb), _p(softplus_rate), float(c_r), _p(a), _p(b),
+                                     T, C, wa_t.shape[0], _stream()), "block_gates")
 
 
-def gated_scan(u: torch.Tensor, r: torch.Tensor, g: torch.Tensor, y: torch.Tensor, y_bias: torch.Tensor | None,
-               softplus_rate: torch.Tensor, c_r: float, state: torch.Tensor, slots: torch.Tensor, cu_q: torch.Tensor,
-               num_seqs: int, out: torch.Tensor) -> torch.Tensor:
-    """a = exp(c_r * r * softplus_rate); S = a S + sqrt(1 - a^2) g u per channel along each request's tokens, S from and
-    back to ``state`` (float32 [slots, C]); out[t] = S * gelu_tanh(y[t] + y_bias).  y: a [T, C] view, float32 or of
-    out's type; out: [T, C] of the run's type."""
-    _need_cuda(u, r, g, y, state, out)
-    C = u.shape[1]
-    if y.stride(1) != 1 or out.stride(1) != 1 or not state.is_contiguous():
+def gated_scan(a: torch.Tensor, b: torch.Tensor, y: torch.Tensor, y_bias: torch.Tensor | None, state: torch.Tensor,
+               slots: torch.Tensor, cu_q: torch.Tensor, num_seqs: int, out: torch.Tensor, work: dict | None = None) -> torch.Tensor:
+    """S = a S + b per channel along each request's tokens, S from and back to ``state`` (float32 [slots, C]);
+    out[t] = S * gelu_tanh(y[t] + y_bias).  y: a [T, C] view, float32 or of out's type; out: [T, C] of the run's type.
+    ``work``: the step's segments (``segment_work``); default: every request's portion is one item."""
+    _need_cuda(a, b, y, state, out)
+    C = a.shape[1]
+    if y.stride(1) != 1 or out.stride(1) != 1 or not state.is_contiguous() or not a.is_contiguous() or not b.is_contiguous():
         raise KernelError("gated_scan: rows of y and out must be dense")
-    _check(library().acv_gated_scan(_p(u), _p(r), _p(g), _p(y), y.stride(0), _p(y_bias), _p(softplus_rate), float(c_r),
-                                    _p(state), _p(slots), _p(cu_q), _p(out), out.stride(0), num_seqs, C,
-                                    dtype_code(y.dtype), dtype_code(out.dtype), _stream()), "gated_scan")
+    seg_seq, seg_idx, seg_len, n_items, summaries = _segments(work, num_seqs)
+    seg = torch.empty((n_items, 2, C), device=a.device, dtype=torch.float32) if summaries else None
+    _check(library().acv_gated_scan(_p(a), _p(b), _p(y), y.stride(0), _p(y_bias), _p(state), _p(slots), _p(cu_q),
+                                    _p(seg_seq), _p(seg_idx), seg_len, _p(seg), 1 if summaries else 0, _p(out),
+                                    out.stride(0), n_items, C, dtype_code(y.dtype), dtype_code(out.dtype), _stream()),
+           "gated_scan")
     return out
 
 
 # ----------------------------------------------------------------------------- retention
 def retention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cos_sin: torch.Tensor | None, positions: torch.Tensor,
               decay: torch.Tensor, k_scale: float, state: torch.Tensor, slots: torch.Tensor, cu_q: torch.Tensor,
-              num_seqs: int, out: torch.Tensor, num_heads: int, dim: int, value_dim: int) -> torch.Tensor:
+              num_seqs: int, out: torch.Tensor, num_heads: int, dim: int, value_dim: int,
+              work: dict | None = None) -> torch.Tensor:
     """S = decay_h S + k v^T, o = S^T q along each request's tokens, per head; q, k ([T, H*dim]) and v ([T, H*value_dim])
     are views of one projection (same row stride); q and k are rotated by ``cos_sin`` (float32 [positions, rot]) and k
-    multiplied by ``k_scale`` in float; state float32 [slots, H, dim, value_dim]; out float32 [T, H*value_dim]."""
+    multiplied by ``k_scale`` in float; state float32 [slots, H, dim, value_dim]; out float32 [T, H*value_dim].
+    ``work``: the step's segments (``segment_work``); default: every request's portion is one item."""
     _need_cuda(q, k, v, state, out)
     if not (q.stride(0) == k.stride(0) == v.stride(0)) or q.stride(1) != 1 or k.stride(1) != 1 or v.stride(1) != 1:
         raise KernelError("retention: q, k and v must be views of one projection with dense rows")
@@ -1345,8 +1384,11 @@ def retention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cos_sin: torch.
         raise KernelError("retention: float32 state and output are wanted")
     rot = cos_sin.shape[1] if cos_sin is not None else 0
     rows = cos_sin.shape[0] if cos_sin is not None else 0
+    seg_seq, seg_idx, seg_len, n_items, summaries = _segments(work, num_seqs)
+    seg = torch.empty((n_items, num_heads, dim, value_dim), device=q.device, dtype=torch.float32) if summaries else None
     _check(library().acv_retention(_p(q), _p(k), _p(v), q.stride(0), _p(cos_sin), rot, rows, _p(positions), _p(decay),
-                                   float(k_scale), _p(state), _p(slots), _p(cu_q), _p(out), out.stride(0), num_seqs,
+                                   float(k_scale), _p(state), _p(slots), _p(cu_q), _p(seg_seq), _p(seg_idx), seg_len,
+                                   _p(seg), 1 if summaries else 0, _p(out), out.stride(0), n_items,
                                    num_heads, dim, value_dim, dtype_code(q.dtype), _stream()), "retention")
     return out
 

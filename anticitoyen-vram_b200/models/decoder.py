@@ -174,9 +174,11 @@ class DecoderModel:
         out = {}
         for block in self.blocks:
             mixer = getattr(block, "mixer", None)
-            key = getattr(mixer, "metadata_key", None)
-            if key is not None and key not in out:
-                out[key] = mixer
+            if hasattr(mixer, "metadata_providers"):
+                for key, provider in mixer.metadata_providers().items():
+                    out.setdefault(key, provider)
+            elif getattr(mixer, "metadata_key", None) is not None:
+                out.setdefault(mixer.metadata_key, mixer)
         return out
 
     def _view(self, storage, slot: int, writes: bool) -> CacheView | None:

@@ -98,6 +98,11 @@ class Mixer(Part):
     # written once into a captured graph's buffer).  Mixers with the same key share one set per step.
     metadata_key: str | None = None
 
+    def metadata_providers(self) -> dict:
+        """{key: the object that offers ``step_metadata`` and ``decode_metadata`` for that key}: this mixer under its
+        ``metadata_key``; a mixer made of several says what each of them asks for."""
+        return {self.metadata_key: self} if self.metadata_key is not None else {}
+
     def cache_need(self):
         """PagedNeed, StateNeed or None: what this mixer keeps for each request; or a dict {name: need} (needs may be
         dicts again) where it keeps several things: its ``CacheView`` then has one view for each name in ``parts``."""

@@ -363,17 +363,9 @@ class ParallelMixers(Mixer):
         for side in (self.left, self.right):
             if not all(hasattr(side, a) for a in ("in_size", "inner_size", "mix")):
                 raise ValueError(f"a '{side.kind}' mixer cannot stand beside another one (it offers no mix())")
-        keys = {k for k in (self.left.metadata_key, self.right.metadata_key) if k is not None}
-        if len(keys) > 1:
-            raise ValueError("mixers side by side may ask for one kind of per-step data between them")
-        self.metadata_key = keys.pop() if keys else None
-        self._provider = self.left if self.left.metadata_key is not None else self.right
 
-    def step_metadata(self, q_lens, kv_lens, cu_q) -> StepMetadata:
-        return self._provider.step_metadata(q_lens, kv_lens, cu_q)
-
-    def decode_metadata(self, padded: int, max_kv: int) -> StepMetadata:
-        return self._provider.decode_metadata(padded, max_kv)
+    def metadata_providers(self) -> dict:
+        return {**self.right.metadata_providers(), **self.left.metadata_providers()}
 
     def cache_need(self):
         needs = {"left": self.left.cache_need(), "right": self.right.cache_need()}

@@ -11,14 +11,27 @@ import torch
 from ..cache.manager import StateNeed
 from ..kernels import ops
 from ..weights.needs import TensorNeed
-from .base import CacheView, Mixer, Runtime
+from .base import CacheView, Mixer, Runtime, StepMetadata
 from .linear import Linear
 from .plan import PartSpec
 from .registry import build, register
 
 
+class SegmentedRecurrence(Mixer):
+    """What the mixers with a linear recurrence ask of every step: the list of (request, segment) items that their
+    kernels run side by side (``ops.segment_work``).  One list serves every such layer of a model."""
+
+    metadata_key = "segments"
+
+    def step_metadata(self, q_lens, kv_lens, cu_q) -> StepMetadata:
+        return StepMetadata(*ops.segment_work(q_lens))
+
+    def decode_metadata(self, padded: int, max_kv: int) -> StepMetadata:
+        return StepMetadata(*ops.segment_work_decode(padded))
+
+
 @register("mixer", "retention")
-class Retention(Mixer):
+class Retention(SegmentedRecurrence):
     """Linear attention with a fixed decay per head, without softmax or denominator:
 
         S_t = decay_h S_{t-1} + k_t v_t^T,   o_t = S_t^T q_t            S: [dim, value_dim] per head, float32
@@ -93,7 +106,8 @@ class Retention(Mixer):
         o = torch.empty((proj.shape[0], self.inner_size), device=proj.device, dtype=torch.float32)
         table = self.position.rotary_table() if self.position is not None else None
         ops.retention(proj[:, :a], proj[:, a:b], proj[:, b:b + self.inner_size], table, ctx.positions, self.decay,
-                      self.k_scale, cache.state, ctx.state_slots[cache.group], ctx.cu_q, ctx.num_seqs, o, H, D, DV)
+                      self.k_scale, cache.state, ctx.state_slots[cache.group], ctx.cu_q, ctx.num_seqs, o, H, D, DV,
+                      work=ctx.work.get(self.metadata_key))
         ops.retention_gate(o, proj[:, b + self.inner_size:], out, H, DV, self.norm_eps, self.out_scale)
 
     def forward(self, h, ctx, cache: CacheView):
@@ -104,7 +118,7 @@ class Retention(Mixer):
 
 
 @register("mixer", "rglru")
-class GatedLinearRecurrence(Mixer):
+class GatedLinearRecurrence(SegmentedRecurrence):
     """The recurrent block of Griffin (De et al., "Griffin: Mixing Gated Linear Recurrences with Local Attention for
     Efficient Language Models"): two branches of ``width`` channels,
 
@@ -186,10 +200,10 @@ class GatedLinearRecurrence(Mixer):
             conv_state, conv_slots = u, ctx.state_slots[cache.parts["state"].group]      # never read: no tap reaches back
         ops.causal_conv(xy[:, :C], self.x_bias, self.conv_w, self.conv_b, conv_state, conv_slots, ctx.cu_q,
                         ctx.seq_of_token, u)
-        r, g = torch.empty_like(u), torch.empty_like(u)
-        ops.block_gates(u, self.wa_t, self.ba, self.wb_t, self.bb, r, g)
+        a, b = torch.empty_like(u), torch.empty_like(u)
+        ops.block_gates(u, self.wa_t, self.ba, self.wb_t, self.bb, self.softplus_lam, -self.rate, a, b)
         st = cache.parts["state"]
         mixed = torch.empty((T, C), device=h.device, dtype=h.dtype)
-        ops.gated_scan(u, r, g, xy[:, C:], self.y_bias, self.softplus_lam, -self.rate, st.state,
-                       ctx.state_slots[st.group], ctx.cu_q, ctx.num_seqs, mixed)
+        ops.gated_scan(a, b, xy[:, C:], self.y_bias, st.state, ctx.state_slots[st.group], ctx.cu_q, ctx.num_seqs, mixed,
+                       work=ctx.work.get(self.metadata_key))
         return self.o(mixed)

@@ -303,6 +303,100 @@ ZOTONEX_SIZES = {
 }
 
 
+REDUDRA_SIZES = {
+    # width; attention: heads, kv heads, head size (keys and values), window, kept first tokens; retention: heads, key size,
+    # value size; recurrence: channels, blocks, taps; feed-forward size
+    "s": dict(width=2048, heads=16, kv_heads=4, dim=128, window=1024, keep=4, r_heads=8, r_dim=64, r_vdim=128,
+              channels=2048, blocks=16, taps=4, ff=6144),
+    "m": dict(width=4096, heads=32, kv_heads=8, dim=128, window=2048, keep=4, r_heads=16, r_dim=64, r_vdim=128,
+              channels=4096, blocks=16, taps=4, ff=12288),
+}
+
+
+def run_redudra(args) -> int:
+    """``--design redudra``: prefill and decode throughput of the Redudra design at layer sizes of real models (random
+    weights; four layers, parallel and recurrent ones in turn), beside a Qwen3 model of equal size: the same width, as
+    many attention heads of the same size, the same feed-forward size.  Whole steps through the step function, and the
+    mixer and feed-forward of a parallel layer and of a recurrent layer alone with their rooflines (L2 flushed before
+    each timed run).  One JSON line."""
+    import torch
+
+    from acvram_b200 import bench as B
+    from acvram_b200.config import Qwen3Config, RedudraConfig
+    from acvram_b200.engine.runner import ModelRunner
+    from acvram_b200.models import build_random
+
+    pk, pk_src = peaks()
+    K, W = args.steps, args.warmup
+    page = 64
+    layers, vocab = args.layers or 4, 32768
+    out = {"design": "redudra", "beside": "qwen3", "layers": layers, "vocab": vocab, "dtype": "bf16", "page_size": page,
+           "data": "synthetic token ids, random weights", "peaks": {**pk, "source": pk_src}, "sizes": {}}
+    for name in args.sizes.split(","):
+        z = REDUDRA_SIZES[name]
+        par = {"type": "parallel", "mlp": {"kind": "dense", "ff": z["ff"]}, "mixer": {
+            "left": {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["dim"], "scale": z["dim"] ** -0.5,
+                     "mask": {"size": z["window"], "keep_first": z["keep"]},
+                     "rot": {"base": 1e6, "dims": z["dim"], "scaling": {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}}},
+            "right": {"heads": z["r_heads"], "dim": z["r_dim"], "vdim": z["r_vdim"],
+                      "decay": [1.0 - 2.0 ** (-5 - 3 * h / z["r_heads"]) for h in range(z["r_heads"])],
+                      "rot": {"base": 1e4, "dims": z["r_dim"]}},
+            "left_scale": 0.6, "right_scale": 0.5}}
+        rec = {"type": "rglru", "mlp": {"kind": "dense", "ff": z["ff"]},
+               "mixer": {"width": z["channels"], "blocks": z["blocks"], "conv": z["taps"]}}
+        rcfg = RedudraConfig.from_dict({"architecture": "Redudra", "vocab": vocab, "width": z["width"], "norm": {"eps": 1e-6},
+                                        "residual_mult": 0.5, "logit_softcap": 30.0,
+                                        "layers": [par if i % 2 == 0 else rec for i in range(layers)]})
+        qcfg = Qwen3Config(vocab_size=vocab, hidden_size=z["width"], intermediate_size=z["ff"], num_hidden_layers=layers,
+                           num_attention_heads=z["heads"], num_key_value_heads=z["kv_heads"], head_dim=z["dim"],
+                           rms_norm_eps=1e-6, rope_theta=1e6, max_position_embeddings=8192, tie_word_embeddings=False)
+        res = {"redudra": dict(z), "qwen3": {"hidden": qcfg.hidden_size, "intermediate": qcfg.intermediate_size,
+                                            "q_heads": qcfg.num_attention_heads, "kv_heads": qcfg.num_key_value_heads,
+                                            "head_dim": qcfg.head_dim}}
+        for arm, cfg in (("redudra", rcfg), ("qwen3", qcfg)):
+            model = build_random(cfg, seed=0, dtype=torch.bfloat16, device="cuda:0")
+            batch_max = 64
+            tokens = batch_max * (args.context + 2 * (K + W) + 2 * page) + 4096
+            runner = ModelRunner(model, page, tokens // page + 8, batch_max + 2, max_len=8192)
+            if not args.no_cuda_graphs:
+                runner.enable_graphs()
+            r = {"weights_gb": round(model.weight_bytes() / 1e9, 3)}
+            try:
+                pre = B.time_prefill(runner, 2048, reps=5, warmup=3)
+                flops = B.prefill_flops(model, 2048)
+                r["prefill_2048"] = {"tokens_per_s": round(pre["tokens_per_s"], 1), "ms": round(pre["ms"], 3),
+                                     "tflops_frac": round(flops / (pre["ms"] * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}
+                for b in (8, 64):
+                    names = [f"d{b}-{i}" for i in range(b)]
+                    B.fill_contexts(runner, names, args.context)
+                    try:
+                        d = B.time_decode(runner, names, K, W)
+                    finally:
+                        for n in names:
+                            runner.release(n)
+                    nbytes = B.decode_step_bytes(model, b, args.context + W + K // 2)
+                    r[f"decode_b{b}"] = {"tokens_per_s": round(d["tokens_per_s"], 1), "ms_per_step": round(d["ms_per_step"], 4),
+                                         "hbm_frac": round(nbytes / (d["ms_per_step"] * 1e-3) / 1e9 / pk["hbm_gbs"], 4)}
+                kinds = (("parallel", 0), ("recurrent", 1)) if arm == "redudra" and layers > 1 else (("", 0),)
+                for kind, layer in kinds:
+                    for label, ql, kl in (("prefill_2048", [2048], [2048]), ("decode_b64", [1] * 64, [args.context] * 64)):
+                        parts = B.time_parts(runner, ql, kl, layer=layer)
+                        for part, v in parts.items():
+                            sec = v["ms"] * 1e-3
+                            r[f"{kind + '_' if kind else ''}{part}_{label}"] = {
+                                "us": round(v["ms"] * 1e3, 1),
+                                "tflops_frac": round(v["flops"] / sec / (pk["bf16_tflops"] * 1e12), 4),
+                                "hbm_frac": round(v["bytes"] / sec / 1e9 / pk["hbm_gbs"], 4)}
+            except B.Refused as exc:
+                r["refused"] = str(exc)
+            res[arm + "_result"] = r
+            del runner, model
+            _free_device_memory()
+        out["sizes"][name] = res
+    print(json.dumps(out))
+    return 0
+
+
 def run_design(args) -> int:
     """``--design zotonex``: prefill and decode throughput of the Zotonex design at layer sizes of real models (random
     weights, a few layers), beside a Qwen3 model of equal size: the same width, as many heads of the same value size,
@@ -404,7 +498,7 @@ def main() -> int:
     ap.add_argument("--page-size", type=int, default=16, help="tokens in a page of the cache (the engine's own default is 64)")
     ap.add_argument("--skip-points", action="store_true", help="skip the batch 1 and 64 points")
     ap.add_argument("--no-cuda-graphs", action="store_true")
-    ap.add_argument("--design", default="", choices=["", "zotonex"],
+    ap.add_argument("--design", default="", choices=["", "zotonex", "redudra"],
                     help="measure another design beside its closest relative instead of the headline (see run_design)")
     ap.add_argument("--sizes", default="s,m", help="with --design: which of its sizes (s: width 2048, m: width 4096)")
     ap.add_argument("--time-limit", type=float, default=240.0,
@@ -417,6 +511,8 @@ def main() -> int:
         args.warmup = 3
     if args.impl == "reference":
         return run_reference(args)
+    if args.design == "redudra":
+        return run_redudra(args)
     if args.design:
         return run_design(args)
     return run_ours(args)

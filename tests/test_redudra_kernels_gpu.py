@@ -58,6 +58,15 @@ def batches(lengths, cuts_of):
     return steps
 
 
+def segments(q_lens, seg_len):
+    """The step's (request, segment) items on the device, for segments of ``seg_len`` tokens (0: none, whole portions)."""
+    from acvram_b200.kernels import ops
+    if not seg_len:
+        return None
+    arrays, values = ops.segment_work(q_lens, seg_len)
+    return {**{k: i32(v) for k, v in arrays.items()}, **values}
+
+
 def step_arrays(step):
     cu = [0]
     seq_of = []
@@ -175,7 +184,8 @@ def test_gates_and_scan_over_steps(C, blocks):
 
     want = [whole(u, y) for u, y in zip(us, ys)]
     wa_t, wb_t = dev(wa.transpose(0, 2, 1)), dev(wb.transpose(0, 2, 1))
-    for cuts in ([[40], CUTS[1], [1]], [[17, 1, 2, 20], CUTS[0], [1]], [[1], CUTS[3], [1]]):
+    for cuts, seg_len in (([[40], CUTS[1], [1]], 0), ([[17, 1, 2, 20], CUTS[0], [1]], 0), ([[1], CUTS[3], [1]], 0),
+                          ([[40], CUTS[2], [1]], 7), ([[25, 15], CUTS[1], [1]], 5), ([[40], CUTS[3], [1]], 40)):
         state = torch.zeros((4, C), device=DEV)
         slots = [2, 3, 0]
         got = [np.zeros((n, C)) for n in lengths]
@@ -183,10 +193,11 @@ def test_gates_and_scan_over_steps(C, blocks):
             cu, _ = step_arrays(step)
             u = dev(np.concatenate([us[r][a:a + c] for r, a, c in step]))
             y = dev(np.concatenate([ys[r][a:a + c] for r, a, c in step]))
-            r_, g_ = torch.empty_like(u), torch.empty_like(u)
-            ops.block_gates(u, wa_t, dev(ba), wb_t, dev(bb), r_, g_)
+            a_, b_ = torch.empty_like(u), torch.empty_like(u)
+            ops.block_gates(u, wa_t, dev(ba), wb_t, dev(bb), dev(sp), -8.0, a_, b_)
             out = torch.empty_like(u)
-            ops.gated_scan(u, r_, g_, y, dev(yb), dev(sp), -8.0, state, i32([slots[r] for r, _, _ in step]), cu, len(step), out)
+            ops.gated_scan(a_, b_, y, dev(yb), state, i32([slots[r] for r, _, _ in step]), cu, len(step), out,
+                           work=segments([c for _, _, c in step], seg_len))
             o = 0
             for r, a, c in step:
                 got[r][a:a + c] = out[o:o + c].cpu().numpy()
@@ -230,7 +241,8 @@ def test_retention_over_steps(H, D, DV, rot, dtype):
         ang = np.arange(128)[:, None] * f[None, :]
         table = dev(np.concatenate([np.cos(ang), np.sin(ang)], axis=1) * mag)
     tol = 3e-5 if dtype == "float32" else 1.2e-2
-    for cuts in ([[70], CUTS[1], [2]], [[33, 1, 16, 2, 18], CUTS[0], [1]], [[1], CUTS[3], [2]]):
+    for cuts, seg_len in (([[70], CUTS[1], [2]], 0), ([[33, 1, 16, 2, 18], CUTS[0], [1]], 0), ([[1], CUTS[3], [2]], 0),
+                          ([[70], CUTS[2], [2]], 16), ([[33, 37], CUTS[1], [2]], 9), ([[70], CUTS[3], [1]], 70)):
         state = torch.zeros((4, H, D, DV), device=DEV)
         slots = [1, 3, 0]
         got = [np.zeros((n, H * DV)) for n in lengths]
@@ -240,7 +252,8 @@ def test_retention_over_steps(H, D, DV, rot, dtype):
             pos = i32([p for r, a, c in step for p in range(a, a + c)])
             o = torch.empty((x.shape[0], H * DV), device=DEV)
             ops.retention(x[:, :H * D], x[:, H * D:2 * H * D], x[:, 2 * H * D:2 * H * D + H * DV], table, pos,
-                          dev(decay), D ** -0.5, state, i32([slots[r] for r, _, _ in step]), cu, len(step), o, H, D, DV)
+                          dev(decay), D ** -0.5, state, i32([slots[r] for r, _, _ in step]), cu, len(step), o, H, D, DV,
+                          work=segments([c for _, _, c in step], seg_len))
             out = torch.empty((x.shape[0], H * DV + 6), device=DEV, dtype=DT[dtype])
             ops.retention_gate(o, x[:, 2 * H * D + H * DV:], out[:, 6:], H, DV, eps, out_scale)
             at = 0
@@ -269,24 +282,26 @@ class Paged:
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("NH,NKV,D,DV,rot,window,keep,page", [
-    (4, 2, 16, 24, 8, 20, 3, 16), (2, 2, 32, 32, 32, 24, 0, 16), (3, 3, 24, 40, 10, 7, 9, 8), (6, 1, 64, 80, 64, 136, 4, 16),
-    (2, 1, 64, 64, 64, 48, 4, 16), (2, 2, 16, 16, 16, 0, 0, 16)])
-def test_rope_append_and_attention_with_planted_keys(NH, NKV, D, DV, rot, window, keep, page, dtype):
+@pytest.mark.parametrize("NH,NKV,D,DV,rot,window,keep,page,n", [
+    (4, 2, 16, 24, 8, 20, 3, 16, 200), (2, 2, 32, 32, 32, 24, 0, 16, 200), (3, 3, 24, 40, 10, 7, 9, 8, 200),
+    (6, 1, 64, 80, 64, 136, 4, 16, 200), (2, 1, 64, 64, 64, 48, 4, 16, 200), (2, 2, 16, 16, 16, 0, 0, 16, 200),
+    (4, 2, 128, 128, 64, 100, 140, 64, 700), (2, 2, 64, 64, 32, 130, 1, 32, 450)])
+def test_rope_append_and_attention_with_planted_keys(NH, NKV, D, DV, rot, window, keep, page, n, dtype):
     """Keys are planted so that, for the last query, one key far back would win the softmax by a wide margin if it were
     seen: at the last kept position and the first one not kept, just inside and just outside the window, at a page's
     first and last row.  Whether it is seen follows the oracle's ``visible``; a kernel that is one off shows."""
     from types import SimpleNamespace
     from acvram_b200.kernels import ops
-    n = 200
     rng = np.random.default_rng(NH * 100 + D)
     rs = {"base": 3000.0, "dims": rot, "scaling": {"factor": 2.0, "original": 64, "fast": 8.0, "slow": 1.0}}
     f, mag = pr.rotary_frequencies(rs)
-    ang = np.arange(256)[:, None] * f[None, :]
+    ang = np.arange(n + 8)[:, None] * f[None, :]
     table = dev(np.concatenate([np.cos(ang), np.sin(ang)], axis=1) * mag)
     scale, v_scale = 0.4, 0.6
     places = sorted({0, max(keep - 1, 0), keep, n - window - 1 if window else 5, n - window if window else 6, n - window + 1 if window else 7,
                      page - 1, page, n - page, n - 2})
+    if n > 200:     # the long cases: the edges alone
+        places = sorted({max(keep - 1, 0), keep, n - window - 1, n - window})
     for place in places:
         x = bf(rng.standard_normal((n, NH * D + NKV * D + NKV * DV)))
         q = x[:, :NH * D].reshape(n, NH, D)
@@ -308,7 +323,7 @@ def test_rope_append_and_attention_with_planted_keys(NH, NKV, D, DV, rot, window
                 w = np.exp(s[i, js] - s[i, js].max())
                 want[i, a] = (w / w.sum()) @ (v[js, g] * v_scale)
         want = want.reshape(n, NH * DV)
-        for cuts in ([n], [n - 1, 1], [37, 2, n - 50, 1, 1, 9]):
+        for cuts in ([n], [n - 1, 1], [37, 2, n - 50, 1, 1, 9], [n - 140, 130, 1] + [1] * 9):
             pc = Paged(n, NKV, D, DV, page, DT[dtype], place)
             got = np.zeros((n, NH * DV))
             at = 0
