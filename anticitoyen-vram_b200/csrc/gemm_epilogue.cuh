@@ -18,6 +18,7 @@ struct GemmParams {
     int act;                // 1: output features come in (gate, up) pairs and C[:, n/2] = silu(gate) * up
                             // 2: the same pairs through a clamped gated unit, scaled by the row first (tokens on rows only):
                             //    g = min(w gate, limit), u = clamp(w up, +-limit), C = g * sigmoid(alpha g) * (u + 1)
+    const float* bias;      // float [N]: added to the product's feature n before anything else is made of it (null: none)
     const float* row_scale; // act 2: w of each row of A (null: 1)
     float glu_limit, glu_alpha;
     // grouped product (tokens on rows): tile ta of A multiplies the rows [tile_expert[ta] * N, +N) of the B operand,
@@ -86,6 +87,22 @@ __device__ __forceinline__ int swiglu_lane_pair(const float (&v)[16], int lane, 
 #pragma unroll
     for (int c = 0; c < 8; ++c) o[c] = swiglu_pair(odd ? other[c] : v[c], odd ? v[c + 8] : other[c]);
     return odd ? 8 : 0;
+}
+
+// The bias of 16 accumulator columns of one tensor-memory lane (row_a, col0 as in gt_store16): features lie on the
+// lanes when the weight is the A operand, on the columns otherwise.
+__device__ __forceinline__ void gt_add_bias(const GemmParams& p, int row_a, int col0, float (&v)[16]) {
+    if (p.swap) {
+        if (row_a < p.N) {
+            const float b = p.bias[row_a];
+#pragma unroll
+            for (int c = 0; c < 16; ++c) v[c] += b;
+        }
+    } else {
+#pragma unroll
+        for (int c = 0; c < 16; ++c)
+            if (col0 + c < p.N) v[c] += p.bias[col0 + c];
+    }
 }
 
 // Write 16 accumulator columns of one tensor-memory lane: row_a is the A-operand row the lane holds,

@@ -396,6 +396,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     float v[16];
 #pragma unroll
                     for (int c = 0; c < 16; ++c) v[c] = __uint_as_float(r[c]);
+                    if (p.bias) gt_add_bias(p, row_a, tb * BN + c0, v);
                     if (p.staged) gt_stage16(p, tiles, wq * 32 + lane, c0, v, lane);
                     else gt_store16(p, row_a, tb * BN + c0, v, lane);
                 }
@@ -464,6 +465,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 #pragma unroll
                         for (int c = 0; c < 16; ++c) sum[c] += v[c];
                     }
+                    if (p.bias) gt_add_bias(p, row_a, tb * BN + c0, sum);
                     gt_store16(p, row_a, tb * BN + c0, sum, lane);
                 }
                 if (et == 0) p.counters[tile] = 0;
@@ -502,6 +504,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 for (int sp = 1; sp < p.splits; ++sp)           // split order: the sum does not depend on timing
 #pragma unroll
                     for (int c = 0; c < 16; ++c) sum[c] += part[((sp - 1) * BN + c0 + c) * GT_BM];
+                if (p.bias) gt_add_bias(p, row_a, tb * BN + c0, sum);
                 if (p.staged) gt_stage16(p, tiles, wq * 32 + lane, c0, sum, lane);
                 else gt_store16(p, row_a, tb * BN + c0, sum, lane);
             }
@@ -679,6 +682,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     float v[16];
 #pragma unroll
                     for (int c = 0; c < 16; ++c) v[c] = __uint_as_float(r[c]);
+                    if (p.bias) gt_add_bias(p, row_a, tb * GP_BN + c0, v);
                     gt_store16(p, row_a, tb * GP_BN + c0, v, lane);
                 }
             }
@@ -866,6 +870,19 @@ ACV_API int acv_gemm_tc(const void* x, int ldx, const void* w, int ldw, void* C,
                         cudaStream_t stream) {
     GemmParams p = {};
     p.qkv = 0;
+    return gemm_tc_run(p, x, ldx, w, ldw, C, ldc, M, N, K, out_f32, act, swap, bn, splits, workspace, workspace_floats,
+                       counters, n_counters, status, sm_count, stages, flags, stream);
+}
+
+// The same with a bias: float [N], added to feature n of the product before the activation (for the paired SiLU form
+// the bias lists the pairs as the weight's rows do).
+ACV_API int acv_gemm_tc_bias(const void* x, int ldx, const void* w, int ldw, void* C, int ldc, int M, int N, int K,
+                             int out_f32, int act, int swap, int bn, int splits, float* workspace, long long workspace_floats,
+                             int* counters, long long n_counters, int* status, int sm_count, int stages, int flags,
+                             const float* bias, cudaStream_t stream) {
+    GemmParams p = {};
+    p.qkv = 0;
+    p.bias = bias;
     return gemm_tc_run(p, x, ldx, w, ldw, C, ldc, M, N, K, out_f32, act, swap, bn, splits, workspace, workspace_floats,
                        counters, n_counters, status, sm_count, stages, flags, stream);
 }

@@ -84,6 +84,7 @@ def _declare(lib: ctypes.CDLL) -> None:
         "acv_gemm_simt": [P, I, P, I, P, I, I, I, I, I, I, P],
         "acv_gemm_tc_qkv": [P, I, P, I, P, I, I, I, I, I, I, I, P, LL, P, LL, P, I, I, I, I, I, I, P, P, F, P, I, P, P, P, I, P, P, P, I, I, P],
         "acv_gemm_tc": [P, I, P, I, P, I, I, I, I, I, I, I, I, I, P, LL, P, LL, P, I, I, I, P],
+        "acv_gemm_tc_bias": [P, I, P, I, P, I, I, I, I, I, I, I, I, I, P, LL, P, LL, P, I, I, I, P, P],
         "acv_attention_decode": [P, I, P, I, P, P, P, P, I, P, P, I, P, I, I, I, I, I, F, I, I, I, P, P, P, LL, LL, LL, I, I, I, I, P],
         "acv_attention_tc": [P, I, I, P, I, P, P, P, P, I, P, P, P, I, P, I, I, I, I, I, F, I, I, I, P, I, P],
         "acv_attention_chunk": [P, I, P, I, P, P, P, P, I, P, P, P, I, P, I, I, I, I, I, F, I, I, I, I, P],
@@ -426,8 +427,9 @@ def gemm_tc_plan(M: int, N: int, K: int, sms: int | None = None, bn_multiple: in
 
 
 def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, plan: tuple | None = None,
-            swiglu_pairs: bool = False, static_weights: bool = False) -> torch.Tensor:
-    """out[M,N] = x[M,K] @ w[N,K]^T on tcgen05; x, w bfloat16, out bfloat16 or float32.
+            swiglu_pairs: bool = False, static_weights: bool = False, bias: torch.Tensor | None = None) -> torch.Tensor:
+    """out[M,N] = x[M,K] @ w[N,K]^T (+ bias) on tcgen05; x, w bfloat16, out bfloat16 or float32; ``bias`` float32 [N],
+    added in the epilogue to the float accumulator (before the activation of the paired form).
 
     ``static_weights``: w was written long before this call (a model's weights), so the kernel may
     read its first tiles while the kernel before it in the stream is still running.
@@ -450,10 +452,15 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, plan: tuple | N
     cluster = plan[4] if len(plan) > 4 else (1 if swap and 1 < splits <= 8 else 0)
     tiles = (-(-N // 128) * -(-M // bn)) if swap else (-(-M // 128) * -(-N // bn))
     ws, cnt, status = _gemm_buffers(x.device, tiles * splits * bn * 128 if splits > 1 else 0, tiles)
-    _check(library().acv_gemm_tc(_p(x), x.stride(0), _p(w), w.stride(0), _p(out), out.stride(0), M, N, K,
-                                 1 if out.dtype == torch.float32 else 0, 1 if swiglu_pairs else 0, swap, bn, splits,
-                                 _p(ws), ws.numel(), _p(cnt),
-                                 cnt.numel(), _p(status), sm_count(x.device), stages, cluster | (2 if static_weights else 0), _stream()), "gemm_tc")
+    args = (_p(x), x.stride(0), _p(w), w.stride(0), _p(out), out.stride(0), M, N, K,
+            1 if out.dtype == torch.float32 else 0, 1 if swiglu_pairs else 0, swap, bn, splits, _p(ws), ws.numel(), _p(cnt),
+            cnt.numel(), _p(status), sm_count(x.device), stages, cluster | (2 if static_weights else 0))
+    if bias is not None:
+        if bias.dtype != torch.float32 or bias.numel() != N or not bias.is_contiguous():
+            raise KernelError("gemm_tc: the bias is a contiguous float32 vector with one entry for each row of the weight")
+        _check(library().acv_gemm_tc_bias(*args, _p(bias), _stream()), "gemm_tc")
+    else:
+        _check(library().acv_gemm_tc(*args, _stream()), "gemm_tc")
     return out
 
 
@@ -919,25 +926,31 @@ def decode_layer(x: torch.Tensor, delta: torch.Tensor | None, delta_out: torch.T
     return delta_out
 
 
-def linear_bf16(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, static_weights: bool = False) -> torch.Tensor:
-    """out = x @ w^T in bfloat16 with float accumulation: the tcgen05 kernel; rows that are not 16-byte
-    aligned (K or a stride no multiple of 8) go to the library product, as all do in the reference."""
+def linear_bf16(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, static_weights: bool = False,
+                bias: torch.Tensor | None = None) -> torch.Tensor:
+    """out = x @ w^T (+ bias) in bfloat16 with float accumulation: the tcgen05 kernel, the bias in its epilogue; rows
+    that are not 16-byte aligned (K or a stride no multiple of 8) go to the library product, as all do in the
+    reference, and a kernel of its own adds the bias."""
     if gemm_tc_takes(x, w):
-        return gemm_tc(x, w, out, static_weights=static_weights)
-    return torch.mm(x, w.t(), out=out)
+        return gemm_tc(x, w, out, static_weights=static_weights, bias=bias)
+    torch.mm(x, w.t(), out=out)
+    return add_bias(out, bias) if bias is not None else out
 
 
 def linear_bf16_swiglu(x: torch.Tensor, w_pairs: torch.Tensor, out: torch.Tensor,
-                       static_weights: bool = False) -> torch.Tensor:
-    """out[M, I] = silu(x @ Wg^T) * (x @ Wu^T) in one kernel; w_pairs [2I, K] holds (gate_i, up_i) in rows 2i, 2i+1."""
-    return gemm_tc(x, w_pairs, out, swiglu_pairs=True, static_weights=static_weights)
+                       static_weights: bool = False, bias: torch.Tensor | None = None) -> torch.Tensor:
+    """out[M, I] = silu(x @ Wg^T + bg) * (x @ Wu^T + bu) in one kernel; w_pairs [2I, K] holds (gate_i, up_i) in rows
+    2i, 2i+1, and ``bias`` (float32 [2I]) their biases in the same order."""
+    return gemm_tc(x, w_pairs, out, swiglu_pairs=True, static_weights=static_weights, bias=bias)
 
 
-def linear_bf16_f32out(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, static_weights: bool = False) -> torch.Tensor:
-    """out (float32) = x @ w^T from bfloat16 operands, accumulated in float32."""
+def linear_bf16_f32out(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, static_weights: bool = False,
+                       bias: torch.Tensor | None = None) -> torch.Tensor:
+    """out (float32) = x @ w^T (+ bias) from bfloat16 operands, accumulated in float32."""
     if gemm_tc_takes(x, w):
-        return gemm_tc(x, w, out, static_weights=static_weights)
-    return gemm_simt(x, w, out)
+        return gemm_tc(x, w, out, static_weights=static_weights, bias=bias)
+    gemm_simt(x, w, out)
+    return add_bias(out, bias) if bias is not None else out
 
 
 # ----------------------------------------------------------------------------- a residual stream kept in float

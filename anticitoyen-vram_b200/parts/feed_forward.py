@@ -56,24 +56,29 @@ class SwiGLU(FeedForward):
         # bfloat16 with 16-byte aligned rows: gate and up rows are interleaved (g0, u0, g1, u1 ...) so that the
         # tensor-core product's epilogue holds each pair together and applies SiLU(gate) * up itself; the
         # stacked product's output [T, 2I] is then never written.  Otherwise: stacked product, then the kernel.
-        # (with a bias on gate or up the pair goes the unfused way: the epilogue adds none)
-        self.fused = rt.dtype == torch.bfloat16 and self.hidden_size % 8 == 0 and gate_b is None and up_b is None
+        # (biases of gate and up are interleaved the same way and join the accumulators in that epilogue)
+        self.fused = rt.dtype == torch.bfloat16 and self.hidden_size % 8 == 0
         if self.fused:
-            self.gate_up = Linear(torch.stack([gate, up], dim=1).reshape(2 * self.intermediate_size, self.hidden_size))
+            pair_bias = None
+            if gate_b is not None or up_b is not None:
+                zeros = torch.zeros(self.intermediate_size, device=rt.device, dtype=torch.float32)
+                pair_bias = torch.stack([gate_b if gate_b is not None else zeros, up_b if up_b is not None else zeros],
+                                        dim=1).reshape(-1)
+            self.gate_up = Linear(torch.stack([gate, up], dim=1).reshape(2 * self.intermediate_size, self.hidden_size), pair_bias)
         else:
             self.gate_up = Linear.stacked([gate, up], [gate_b, up_b])
         self.down = Linear(w("down"), down_b)
 
     def decode_layer_spec(self):
         """What the fused decode-layer kernel needs of this feed-forward: gate and up rows interleaved, no biases."""
-        if not self.fused or self.down.bias is not None:
+        if not self.fused or self.down.bias is not None or self.gate_up.bias is not None:
             return None
         return {"intermediate_size": self.intermediate_size, "w_gate_up_pairs": self.gate_up.weight, "w_down": self.down.weight}
 
     def forward(self, h, ctx):
         if self.fused and h.shape[0] and ops.gemm_tc_takes(h, self.gate_up.weight):
             act = torch.empty((h.shape[0], self.intermediate_size), device=h.device, dtype=h.dtype)
-            ops.linear_bf16_swiglu(h, self.gate_up.weight, act, static_weights=True)
+            ops.linear_bf16_swiglu(h, self.gate_up.weight, act, static_weights=True, bias=self.gate_up.bias)
             return self.down(act)
         if self.fused:      # an input the tensor-core kernel does not take: undo the interleaving for this call
             gu = self.gate_up(h).view(h.shape[0], self.intermediate_size, 2).transpose(1, 2).reshape(h.shape[0], -1)

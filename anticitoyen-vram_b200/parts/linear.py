@@ -8,8 +8,9 @@ exception in both: bfloat16 operands, accumulated and returned in float32
 (acvram/engine/model.py:369-410), by a kernel of this package.
 
 A bias is there when the weight file holds one, as in the reference
-(acvram/engine/loader.py:269-270); it is kept in float32 and added by a kernel of
-its own after the product.
+(acvram/engine/loader.py:269-270); it is kept in float32 and added to the float
+accumulator in the tensor-core product's epilogue, or by a kernel of its own
+after the products that have no such epilogue.
 """
 
 from __future__ import annotations
@@ -62,12 +63,12 @@ class Linear:
             return out
         if x.dtype == torch.float32:
             ops.gemm_simt(x, w, out)
+            if self.bias is not None:
+                ops.add_bias(out, self.bias)
         elif out_dtype == torch.float32 and plan is not None and ops.gemm_tc_takes(x, w):
-            ops.gemm_tc(x, w, out, plan=plan, static_weights=True)
+            ops.gemm_tc(x, w, out, plan=plan, static_weights=True, bias=self.bias)
         elif out_dtype == torch.float32:
-            ops.linear_bf16_f32out(x, w, out, static_weights=True)
+            ops.linear_bf16_f32out(x, w, out, static_weights=True, bias=self.bias)
         else:
-            ops.linear_bf16(x, w, out, static_weights=True)
-        if self.bias is not None:
-            ops.add_bias(out, self.bias)
+            ops.linear_bf16(x, w, out, static_weights=True, bias=self.bias)      # (the tensor-core product adds it itself)
         return out

@@ -341,3 +341,27 @@ def test_rope_append_and_attention_with_planted_keys(NH, NKV, D, DV, rot, window
                 got[at:at + c] = out.float().cpu().numpy()
                 at += c
             close(got, want, 3e-5 if dtype == "float32" else 4e-2, f"planted at {place}, cuts {cuts}")
+
+
+# --------------------------------------------------------------------------- the tensor-core product with a bias
+@pytest.mark.parametrize("M", [1, 8, 33, 200, 2048])
+@pytest.mark.parametrize("N,K", [(96, 64), (512, 256), (2048, 2048), (1000, 4096)])
+def test_tensor_core_product_adds_its_bias(M, N, K):
+    """Few tokens (weights on the tensor core's rows, split K, tiles staged in shared memory) and many (tokens on the
+    rows, pairs of CTAs): the bias joins the float accumulator in every epilogue, also in front of the paired SiLU."""
+    from acvram_b200.kernels import ops
+    g = torch.Generator(device="cpu").manual_seed(M * 7 + N)
+    x = (torch.randn(M, K, generator=g) * 0.5).to(torch.bfloat16).to(DEV)
+    w = (torch.randn(N, K, generator=g) / math.sqrt(K)).to(torch.bfloat16).to(DEV)
+    bias = (torch.randn(N, generator=g) * 2.0).to(DEV)
+    want = x.float() @ w.float().t() + bias
+    for dtype in (torch.bfloat16, torch.float32):
+        out = torch.empty(M, N, device=DEV, dtype=dtype)
+        ops.gemm_tc(x, w, out, bias=bias)
+        close(out, want.double().cpu().numpy(), 1e-2 if dtype == torch.bfloat16 else 2e-5, f"plain, {dtype}")
+    gate, up = want[:, 0::2], want[:, 1::2]
+    r = lambda t: t.to(torch.bfloat16).float()
+    paired = r(r(torch.nn.functional.silu(r(gate))) * r(up))
+    out = torch.empty(M, N // 2, device=DEV, dtype=torch.bfloat16)
+    ops.gemm_tc(x, w, out, swiglu_pairs=True, bias=bias)
+    close(out, paired.double().cpu().numpy(), 2e-2, "paired")
