@@ -15,8 +15,8 @@
 //
 // The recurrence is linear in S, so a long portion is cut into segments of seg_len tokens that run side by side
 // (the step's list of (request, segment) items): a first launch leaves each segment's (product of a, state reached
-// from zero; the first segment starts from the request's state), a second one folds what lies before its segment
-// and walks it again, writing the outputs.  Steps of short portions and single tokens run the second launch alone.
+// from zero; the first segment starts from the request's state), a small one folds them into what lies in front of
+// every segment, and a last one walks the segments again from there, writing the outputs.  Steps of short portions and single tokens run the second launch alone.
 #include "common.cuh"
 
 // ----------------------------------------------------------------------------- short causal convolution per channel
@@ -81,50 +81,55 @@ ACV_API int acv_causal_conv(const void* x, int ldx, const float* xb, const float
 
 // ----------------------------------------------------------------------------- the two gates, block-diagonal
 // wa, wb: [blocks][in][out] (transposed when loaded, so that the threads of a warp read neighbouring outputs).
-// grid (token tiles of GT, blocks); a thread owns outputs o, o + blockDim, ... of its block for all tokens of the tile.
-#define GT 16
-
+// grid (token tiles of GT, blocks, tiles of 64 outputs); a thread owns one output of its block for all tokens of the
+// tile.  The tile's inputs wait in shared memory as [in][token], so that a thread reads the GT tokens of an input as
+// vectors of four (one shared-memory instruction to eight multiply-adds).
+template <int GT>
 __global__ void block_gates_kernel(const float* __restrict__ u, const float* __restrict__ wa, const float* __restrict__ ba,
                                    const float* __restrict__ wb, const float* __restrict__ bb,
                                    const float* __restrict__ sp, float c_r, float* __restrict__ r,
                                    float* __restrict__ g, int T, int C, int BW) {
-    extern __shared__ float su[];          // [GT][BW]
+    extern __shared__ __align__(16) float su[];          // [BW][GT]
     pdl_launch_dependents();
     pdl_wait();
     const int t0 = blockIdx.x * GT, blk = blockIdx.y;
     const int nt = min(GT, T - t0);
     for (int i = threadIdx.x; i < GT * BW; i += blockDim.x) {
         const int tt = i / BW, e = i - tt * BW;
-        su[i] = tt < nt ? u[(size_t)(t0 + tt) * C + blk * BW + e] : 0.f;
+        su[e * GT + tt] = tt < nt ? u[(size_t)(t0 + tt) * C + blk * BW + e] : 0.f;
     }
     __syncthreads();
-    const float* wa_b = wa + (size_t)blk * BW * BW;
-    const float* wb_b = wb + (size_t)blk * BW * BW;
-    for (int o = threadIdx.x; o < BW; o += blockDim.x) {
-        float ar[GT], ag[GT];
+    const int o = blockIdx.z * blockDim.x + threadIdx.x;
+    if (o >= BW) return;
+    const float* wa_b = wa + (size_t)blk * BW * BW + o;
+    const float* wb_b = wb + (size_t)blk * BW * BW + o;
+    float ar[GT], ag[GT];
 #pragma unroll
-        for (int tt = 0; tt < GT; ++tt) ar[tt] = ag[tt] = 0.f;
-        for (int i = 0; i < BW; ++i) {
-            const float a = wa_b[(size_t)i * BW + o], b = wb_b[(size_t)i * BW + o];
+    for (int tt = 0; tt < GT; ++tt) ar[tt] = ag[tt] = 0.f;
+#pragma unroll 4
+    for (int i = 0; i < BW; ++i) {
+        const float a = wa_b[(size_t)i * BW], b = wb_b[(size_t)i * BW];
+        const float4* x4 = reinterpret_cast<const float4*>(su + i * GT);
 #pragma unroll
-            for (int tt = 0; tt < GT; ++tt) {
-                const float x = su[tt * BW + i];
-                ar[tt] = fmaf(a, x, ar[tt]);
-                ag[tt] = fmaf(b, x, ag[tt]);
-            }
+        for (int q = 0; q < GT / 4; ++q) {
+            const float4 x = x4[q];
+            ar[4 * q] = fmaf(a, x.x, ar[4 * q]); ar[4 * q + 1] = fmaf(a, x.y, ar[4 * q + 1]);
+            ar[4 * q + 2] = fmaf(a, x.z, ar[4 * q + 2]); ar[4 * q + 3] = fmaf(a, x.w, ar[4 * q + 3]);
+            ag[4 * q] = fmaf(b, x.x, ag[4 * q]); ag[4 * q + 1] = fmaf(b, x.y, ag[4 * q + 1]);
+            ag[4 * q + 2] = fmaf(b, x.z, ag[4 * q + 2]); ag[4 * q + 3] = fmaf(b, x.w, ag[4 * q + 3]);
         }
-        const int ch = blk * BW + o;
-        const float b1 = ba ? ba[ch] : 0.f, b2 = bb ? bb[ch] : 0.f;
-        const float rate = c_r * sp[ch];
+    }
+    const int ch = blk * BW + o;
+    const float b1 = ba ? ba[ch] : 0.f, b2 = bb ? bb[ch] : 0.f;
+    const float rate = c_r * sp[ch];
 #pragma unroll
-        for (int tt = 0; tt < GT; ++tt) {
-            if (tt < nt) {
-                const float rr = 1.f / (1.f + expf(-(ar[tt] + b1)));
-                const float gg = 1.f / (1.f + expf(-(ag[tt] + b2)));
-                const float la = rate * rr;                    // log a <= 0
-                r[(size_t)(t0 + tt) * C + ch] = expf(la);
-                g[(size_t)(t0 + tt) * C + ch] = sqrtf(fmaxf(-expm1f(2.f * la), 0.f)) * gg * su[tt * BW + o];
-            }
+    for (int tt = 0; tt < GT; ++tt) {
+        if (tt < nt) {
+            const float rr = 1.f / (1.f + expf(-(ar[tt] + b1)));
+            const float gg = 1.f / (1.f + expf(-(ag[tt] + b2)));
+            const float la = rate * rr;                    // log a <= 0
+            r[(size_t)(t0 + tt) * C + ch] = expf(la);
+            g[(size_t)(t0 + tt) * C + ch] = sqrtf(fmaxf(-expm1f(2.f * la), 0.f)) * gg * su[o * GT + tt];
         }
     }
 }
@@ -135,16 +140,21 @@ ACV_API int acv_block_gates(const float* u, const float* wa, const float* ba, co
     if (T <= 0) return 0;
     if (blocks <= 0 || C % blocks) return ACV_ERR_SIZE;
     const int BW = C / blocks;
-    const size_t smem = (size_t)GT * BW * sizeof(float);
+    const int gt = T <= 512 ? 4 : 16;       // few tokens: small tiles, so that the grid still fills the device
+    const size_t smem = (size_t)gt * BW * sizeof(float);
     if (smem > 200 * 1024) return ACV_ERR_SIZE;
+    static AcvSmemConfig cfg4, cfg16;
     if (smem > 48 * 1024) {
-        static AcvSmemConfig cfg;
-        const int e = acv_ensure_smem(cfg, block_gates_kernel, (int)smem);
+        const int e = gt == 4 ? acv_ensure_smem(cfg4, block_gates_kernel<4>, (int)smem)
+                              : acv_ensure_smem(cfg16, block_gates_kernel<16>, (int)smem);
         if (e) return e;
     }
-    dim3 grid((T + GT - 1) / GT, blocks);
-    const int threads = BW >= 256 ? 256 : (BW >= 128 ? 128 : (BW > 32 ? 64 : 32));
-    acv_launch(PDL_MISC, block_gates_kernel, grid, threads, smem, stream, u, wa, ba, wb, bb, sp, c_r, r, g, T, C, BW);
+    const int threads = BW >= 64 ? 64 : 32;
+    dim3 grid((T + gt - 1) / gt, blocks, (BW + threads - 1) / threads);
+    if (gt == 4)
+        acv_launch(PDL_MISC, block_gates_kernel<4>, grid, threads, smem, stream, u, wa, ba, wb, bb, sp, c_r, r, g, T, C, BW);
+    else
+        acv_launch(PDL_MISC, block_gates_kernel<16>, grid, threads, smem, stream, u, wa, ba, wb, bb, sp, c_r, r, g, T, C, BW);
     return acv_launch_status();
 }
 
@@ -158,14 +168,36 @@ __device__ __forceinline__ float gelu_tanh_f32(float z) {
 // tokens cu_q[seq] + z * seg_len .. (seg_len of them, or what is left).
 #define SC 8
 
-// what lies in front of segment z of a request whose first segment is item `first`: the fold of the segments' (A, B)
-__device__ __forceinline__ float fold_segments(const float* __restrict__ seg, int first, int z, int C, int c) {
-    float S = seg[((size_t)first * 2 + 1) * C + c];            // the first segment began at the request's state
-    for (int zz = 1; zz < z; ++zz) {
-        const float* e = seg + (size_t)(first + zz) * 2 * C;
-        S = fmaf(e[c], S, e[C + c]);
+// Between the two launches: the entries (A, B) of a request's segments become, in their B, the states in front of the
+// segments that follow: S_in(z + 1) = A(z) S_in(z) + B(z), in place.  grid (items, channel tiles); the block of a
+// request's first segment walks the request's entries.
+__global__ void scan_fold_kernel(float* __restrict__ seg, const int* __restrict__ seg_seq, const int* __restrict__ seg_idx,
+                                 int seg_len, const int* __restrict__ cu_q, int C) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int item = blockIdx.x;
+    const int c = blockIdx.y * blockDim.x + threadIdx.x;
+    if (c >= C || seg_idx[item] != 0) return;
+    const int seq = seg_seq[item];
+    const int nseg = (cu_q[seq + 1] - cu_q[seq] + seg_len - 1) / seg_len;
+    float S = seg[((size_t)item * 2 + 1) * C + c];              // the first segment began at the request's state
+    for (int z0 = 1; z0 < nseg - 1; z0 += 8) {                  // eight entries' loads at a time
+        float A[8], B[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            const float* e = seg + (size_t)(item + z0 + k) * 2 * C;
+            const bool in = z0 + k < nseg - 1;
+            A[k] = in ? e[c] : 0.f;
+            B[k] = in ? e[C + c] : 0.f;
+        }
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            if (z0 + k < nseg - 1) {
+                S = fmaf(A[k], S, B[k]);
+                seg[((size_t)(item + z0 + k) * 2 + 1) * C + c] = S;
+            }
+        }
     }
-    return S;
 }
 
 // SUMMARY: leave (A, B) of the segment in seg[item] and write no output (the last segment of a request does nothing)
@@ -196,7 +228,7 @@ __global__ void gated_scan_kernel(const float* __restrict__ a, const float* __re
         S = (SUMMARY || last) ? *st : seg[((size_t)last_item * 2) * C + c];
         if (SUMMARY) seg[((size_t)last_item * 2) * C + c] = S;
     } else {
-        S = SUMMARY ? 0.f : fold_segments(seg, item - z, z, C, c);
+        S = SUMMARY ? 0.f : seg[((size_t)(item - 1) * 2 + 1) * C + c];     // what lies in front, after the fold
     }
     float A = 1.f;
     const float bias_y = yb ? yb[c] : 0.f;
@@ -238,9 +270,11 @@ ACV_API int acv_gated_scan(const float* a, const float* b, const void* y, int ld
     dim3 grid(n_items, (C + 63) / 64);
 #define SCAN_LAUNCH(TY, T)                                                                                           \
     {                                                                                                                \
-        if (summaries)                                                                                               \
+        if (summaries) {                                                                                             \
             acv_launch(PDL_MISC, gated_scan_kernel<TY, T, true>, grid, 64, 0, stream, a, b, (const TY*)y, ldy, yb, state, \
                        slots, cu_q, seg_seq, seg_idx, seg_len, seg, (T*)out, ldo, C);                               \
+            acv_launch(PDL_MISC, scan_fold_kernel, grid, 64, 0, stream, seg, seg_seq, seg_idx, seg_len, cu_q, C);    \
+        }                                                                                                            \
         acv_launch(PDL_MISC, gated_scan_kernel<TY, T, false>, grid, 64, 0, stream, a, b, (const TY*)y, ldy, yb, state,    \
                    slots, cu_q, seg_seq, seg_idx, seg_len, seg, (T*)out, ldo, C);                                   \
         return acv_launch_status();                                                                                  \

@@ -8,15 +8,19 @@
 // brings each head's o to unit RMS (no weight), multiplies by silu(gate) and a constant, and rounds once.
 //
 // acv_retention: grid (items, heads).  The block's threads are G groups of DV: thread (g, c) keeps rows
-// g*R .. g*R+R-1 of column c of S in registers, walks its tokens in chunks of TC (q, k, v staged in shared memory,
+// g*R .. g*R+R-1 of column c of S in registers (R as large as the registers allow, up to 64: a thread that holds a
+// whole column needs no other thread for its sums, and a block of DV threads leaves room for several blocks on an SM), walks its tokens in chunks of TC (q, k, v staged in shared memory,
 // the partial sums of the chunk reduced over the groups afterwards), and writes S back.
 //
 // The recurrence is linear in S, so a long portion is cut into segments of seg_len tokens that run side by side (the
 // step's list of (request, segment) items): a first launch leaves the state that each segment reaches from zero (the
 // first one from the request's state), without outputs; a second one folds what lies before its segment,
-// S_in(z) = decay^seg_len S_in(z-1) + S_seg(z-1), and walks the segment again with outputs.  Steps of short portions and
+// S_in(z) = decay^seg_len S_in(z-1) + S_seg(z-1) (a small launch of its own between the two), and walks the segment again with outputs.  Steps of short portions and
 // single tokens run the second launch alone.
 #include "common.cuh"
+#include <stdlib.h>
+
+#define RET_WANT_THREADS 512
 
 // the most threads of a block by the rows a thread keeps: the registers of the whole block have to fit an SM's file
 constexpr int ret_max_threads(int R) { return R <= 16 ? 1024 : (R <= 32 ? 512 : 256); }
@@ -71,11 +75,8 @@ __global__ void __launch_bounds__(ret_max_threads(R)) retention_kernel(const T* 
                 s0 = (SUMMARY || last) ? st[at] : keep[at];
                 if (SUMMARY) keep[at] = s0;
             } else if (!SUMMARY) {
-                // what lies in front of this segment: the first segment began at the request's state
-                const float* e = sg.state + ((size_t)(item - z) * H + h) * HS + at;
-                s0 = *e;
-                const float dec_len = exp2f((float)sg.len * log2f(dec));
-                for (int zz = 1; zz < z; ++zz) s0 = fmaf(dec_len, s0, e[(size_t)zz * H * HS]);
+                // what lies in front of this segment: the entry of the segment before, after acv_retention's fold
+                s0 = sg.state[((size_t)(item - 1) * H + h) * HS + at];
             }
         }
         S[i] = s0;
@@ -150,6 +151,38 @@ __global__ void __launch_bounds__(ret_max_threads(R)) retention_kernel(const T* 
     }
 }
 
+// Between the two launches: the entries of a request's segments, each the state its segment reaches from zero (the
+// first one from the request's state), become the states in front of the segments that follow,
+// S_in(z + 1) = decay^seg_len S_in(z) + entry(z), in place.  grid (items, heads, tiles of 256 elements); the blocks of a
+// request's first segment walk the request's entries, a thread one element, eight entries' loads at a time.
+__global__ void retention_fold_kernel(RetSegments sg, const int* __restrict__ cu_q, const float* __restrict__ decay, int H, int HS) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int item = blockIdx.x, h = blockIdx.y;
+    if (sg.idx[item] != 0) return;
+    const int seq = sg.seq[item];
+    const int nseg = (cu_q[seq + 1] - cu_q[seq] + sg.len - 1) / sg.len;
+    if (nseg < 3) return;           // the entry of a first segment already is what lies in front of the second
+    const float dec_len = exp2f((float)sg.len * log2f(decay[h]));
+    float* e = sg.state + ((size_t)item * H + h) * HS;
+    const size_t step = (size_t)H * HS;
+    const int i = blockIdx.z * blockDim.x + threadIdx.x;
+    if (i >= HS) return;
+    float s = e[i];
+    for (int z0 = 1; z0 < nseg - 1; z0 += 8) {
+        float v[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) v[k] = z0 + k < nseg - 1 ? e[(z0 + k) * step + i] : 0.f;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            if (z0 + k < nseg - 1) {
+                s = fmaf(dec_len, s, v[k]);
+                e[(z0 + k) * step + i] = s;
+            }
+        }
+    }
+}
+
 template <typename T, int R>
 static int launch_retention(const void* q, const void* k, const void* v, int ld, const float* cos_sin, int rot,
                             int table_rows, const int* positions, const float* decay, float k_scale, float* state,
@@ -159,7 +192,7 @@ static int launch_retention(const void* q, const void* k, const void* v, int ld,
     const int threads = ((G * DV + 31) / 32) * 32;
     const size_t per_token = (size_t)(2 * D + DV + G * DV) * sizeof(float);
     int TC = (int)((48 * 1024) / per_token);
-    TC = TC > 16 ? 16 : TC;
+    TC = TC > 32 ? 32 : TC;
     if (TC < 1) TC = 1;
     const size_t smem = per_token * TC;
     if (smem > 200 * 1024) return ACV_ERR_SIZE;
@@ -169,9 +202,11 @@ static int launch_retention(const void* q, const void* k, const void* v, int ld,
         if (!e && summaries) e = acv_ensure_smem(cfg_s, retention_kernel<T, R, true>, (int)smem);
         if (e) return e;
     }
-    if (summaries)
+    if (summaries) {
         acv_launch(PDL_ATTN, retention_kernel<T, R, true>, dim3(num_seqs, H), threads, smem, stream, (const T*)q, (const T*)k,
                    (const T*)v, ld, cos_sin, rot, table_rows, positions, decay, k_scale, state, slots, cu_q, sg, o, ldo, H, D, DV, G, TC);
+        acv_launch(PDL_ATTN, retention_fold_kernel, dim3(num_seqs, H, (D * DV + 255) / 256), 256, 0, stream, sg, cu_q, decay, H, D * DV);
+    }
     acv_launch(PDL_ATTN, retention_kernel<T, R, false>, dim3(num_seqs, H), threads, smem, stream, (const T*)q, (const T*)k,
                (const T*)v, ld, cos_sin, rot, table_rows, positions, decay, k_scale, state, slots, cu_q, sg, o, ldo, H, D, DV, G, TC);
     return acv_launch_status();
@@ -208,8 +243,17 @@ ACV_API int acv_retention(const void* q, const void* k, const void* v, int ld, c
     if (seg_len <= 0 || (summaries && (!seg_seq || !seg_idx || !seg_state))) return ACV_ERR_SIZE;
     RetSegments sg;
     sg.seq = seg_seq; sg.idx = seg_idx; sg.len = seg_len; sg.state = seg_state;
+    // rows of the state that a thread keeps: the fewest that let the block fit `want` threads (measured on a B200 at
+    // 64 x 128 per head: blocks of 1024, 512 and 128 threads, see the design notes); ACVRAM_RETENTION_ROWS forces a choice
+    static const int forced = getenv("ACVRAM_RETENTION_ROWS") ? atoi(getenv("ACVRAM_RETENTION_ROWS")) : 0;
     int R = 4;
-    while (R <= 64 && ((D + R - 1) / R) * DV > ret_max_threads(R)) R *= 2;
+    while (R <= 64 && ((D + R - 1) / R) * DV > (ret_max_threads(R) < RET_WANT_THREADS ? ret_max_threads(R) : RET_WANT_THREADS)) R *= 2;
+    if (R > 64) {       // no such block: the most threads that the registers allow
+        R = 4;
+        while (R <= 64 && ((D + R - 1) / R) * DV > ret_max_threads(R)) R *= 2;
+    }
+    if (forced == 4 || forced == 8 || forced == 16 || forced == 32 || forced == 64)
+        if (((D + forced - 1) / forced) * DV <= ret_max_threads(forced)) R = forced;
     if (R > 64) return ACV_ERR_SIZE;      // (a state of more than 64 x 256 elements per head is not built)
     if (dtype == ACV_F32)
         return retention_by_rows<float>(R, q, k, v, ld, cos_sin, rot, table_rows, positions, decay, k_scale, state, slots,

@@ -1321,7 +1321,7 @@ def causal_conv(x: torch.Tensor, x_bias: torch.Tensor | None, taps: torch.Tensor
     return out
 
 
-SEGMENT_TOKENS = 128    # tokens of a segment of a long portion in the kernels of the linear recurrences
+SEGMENT_TOKENS = 64     # tokens of a segment of a long portion in the kernels of the linear recurrences
 
 
 def segment_work(q_lens, seg_len: int = SEGMENT_TOKENS) -> tuple[dict, dict]:
