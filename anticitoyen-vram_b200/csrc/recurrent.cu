@@ -17,7 +17,7 @@
 // (the step's list of (request, segment) items): a first launch leaves each segment's (product of a, state reached
 // from zero; the first segment starts from the request's state), a small one folds them into what lies in front of
 // every segment, and a last one walks the segments again from there, writing the outputs.  Steps of short portions and single tokens run the second launch alone.
-#include "common.cuh"
+#include "mma_tiles.cuh"
 
 // ----------------------------------------------------------------------------- short causal convolution per channel
 // grid (tokens, channel tiles).  The tokens that reach back into the state (the first K-1 of a request's portion)
@@ -155,6 +155,97 @@ ACV_API int acv_block_gates(const float* u, const float* wa, const float* ba, co
         acv_launch(PDL_MISC, block_gates_kernel<4>, grid, threads, smem, stream, u, wa, ba, wb, bb, sp, c_r, r, g, T, C, BW);
     else
         acv_launch(PDL_MISC, block_gates_kernel<16>, grid, threads, smem, stream, u, wa, ba, wb, bb, sp, c_r, r, g, T, C, BW);
+    return acv_launch_status();
+}
+
+// The same on the tensor cores, for runs whose projections are bfloat16: the inputs u are rounded to bfloat16 for the
+// two products (float accumulation); sigmoid, decay and b stay float and b takes the unrounded u.  wa, wb: bfloat16
+// [blocks][out][in] as the weight file has them.  grid (tiles of 64 tokens, blocks, tiles of 64 outputs), four warps
+// of 16 tokens; the tile of u and the weights' 2 x 64 rows wait in shared memory with rows padded by 16 bytes.
+__global__ void __launch_bounds__(128) block_gates_mma_kernel(const float* __restrict__ u, const bf16* __restrict__ wa,
+                                                             const float* __restrict__ ba, const bf16* __restrict__ wb,
+                                                             const float* __restrict__ bb, const float* __restrict__ sp,
+                                                             float c_r, float* __restrict__ r, float* __restrict__ g,
+                                                             int T, int C, int BW) {
+    extern __shared__ __align__(16) unsigned char gm_smem[];
+    const int LD = BW + 8;                                      // elements of a padded row
+    bf16* As = reinterpret_cast<bf16*>(gm_smem);                // [64][LD]
+    bf16* Bs = As + 64 * LD;                                    // [2][64][LD]
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t0 = blockIdx.x * 64, blk = blockIdx.y, o0 = blockIdx.z * 64;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    for (int i = tid; i < 64 * BW; i += 128) {
+        const int tt = i / BW, e = i - tt * BW;
+        As[tt * LD + e] = __float2bfloat16_rn(t0 + tt < T ? u[(size_t)(t0 + tt) * C + blk * BW + e] : 0.f);
+    }
+    const int chunks = BW / 8;                                  // 16-byte pieces of a weight row
+    for (int i = tid; i < 2 * 64 * chunks; i += 128) {
+        const int q = i / (64 * chunks), rem = i - q * 64 * chunks;
+        const int row = rem / chunks, ch = rem - row * chunks;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (o0 + row < BW)
+            v = *reinterpret_cast<const uint4*>((q ? wb : wa) + ((size_t)blk * BW + o0 + row) * BW + ch * 8);
+        *reinterpret_cast<uint4*>(Bs + ((size_t)q * 64 + row) * LD + ch * 8) = v;
+    }
+    __syncthreads();
+    const int gr = lane >> 2, tq = lane & 3;
+    float acc[2][8][4];
+#pragma unroll
+    for (int q = 0; q < 2; ++q)
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) acc[q][j][e] = 0.f;
+    const bf16* a_row = As + (warp * 16 + gr) * LD + 2 * tq;
+    for (int k0 = 0; k0 < BW; k0 += 16) {
+        uint32_t a[4];
+        a[0] = *reinterpret_cast<const uint32_t*>(a_row + k0);
+        a[1] = *reinterpret_cast<const uint32_t*>(a_row + 8 * LD + k0);
+        a[2] = *reinterpret_cast<const uint32_t*>(a_row + k0 + 8);
+        a[3] = *reinterpret_cast<const uint32_t*>(a_row + 8 * LD + k0 + 8);
+#pragma unroll
+        for (int q = 0; q < 2; ++q)
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const bf16* b_row = Bs + ((size_t)q * 64 + j * 8 + gr) * LD + k0 + 2 * tq;
+                mma_bf16(acc[q][j], a, *reinterpret_cast<const uint32_t*>(b_row), *reinterpret_cast<const uint32_t*>(b_row + 8));
+            }
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int t = t0 + warp * 16 + gr + (e >> 1) * 8;
+            const int o = o0 + j * 8 + 2 * tq + (e & 1);
+            if (t < T && o < BW) {
+                const int ch = blk * BW + o;
+                const float rr = 1.f / (1.f + expf(-(acc[0][j][e] + (ba ? ba[ch] : 0.f))));
+                const float gg = 1.f / (1.f + expf(-(acc[1][j][e] + (bb ? bb[ch] : 0.f))));
+                const float la = c_r * sp[ch] * rr;
+                r[(size_t)t * C + ch] = expf(la);
+                g[(size_t)t * C + ch] = sqrtf(fmaxf(-expm1f(2.f * la), 0.f)) * gg * u[(size_t)t * C + ch];
+            }
+        }
+}
+
+// takes blocks whose width is a multiple of 16 up to 256 and 16-byte aligned weights
+ACV_API int acv_block_gates_mma(const float* u, const void* wa, const float* ba, const void* wb, const float* bb,
+                                const float* sp, float c_r, float* r, float* g, int T, int C, int blocks, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (blocks <= 0 || C % blocks) return ACV_ERR_SIZE;
+    const int BW = C / blocks;
+    if (BW % 16 || BW > 256) return ACV_ERR_SIZE;
+    if (((uintptr_t)wa & 15) || ((uintptr_t)wb & 15)) return ACV_ERR_ALIGN;
+    const int smem = 3 * 64 * (BW + 8) * 2;
+    static AcvSmemConfig cfg;
+    if (smem > 48 * 1024) {
+        const int e = acv_ensure_smem(cfg, block_gates_mma_kernel, smem);
+        if (e) return e;
+    }
+    dim3 grid((T + 63) / 64, blocks, (BW + 63) / 64);
+    acv_launch(PDL_MISC, block_gates_mma_kernel, grid, 128, smem, stream, u, (const bf16*)wa, ba, (const bf16*)wb, bb, sp, c_r,
+               r, g, T, C, BW);
     return acv_launch_status();
 }
 

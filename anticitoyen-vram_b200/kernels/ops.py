@@ -78,6 +78,7 @@ def _declare(lib: ctypes.CDLL) -> None:
         "acv_softcap_f32": [P, LL, F, P],
         "acv_causal_conv": [P, I, P, P, P, P, P, P, P, P, I, I, I, I, P],
         "acv_block_gates": [P, P, P, P, P, P, F, P, P, I, I, I, P],
+        "acv_block_gates_mma": [P, P, P, P, P, P, F, P, P, I, I, I, P],
         "acv_gated_scan": [P, P, P, I, P, P, P, P, P, P, I, P, I, P, I, I, I, I, I, P],
         "acv_retention": [P, P, P, I, P, I, I, P, P, F, P, P, P, P, P, I, P, I, P, I, I, I, I, I, I, P],
         "acv_retention_gate": [P, I, P, I, P, I, I, I, I, F, F, I, P],
@@ -1351,14 +1352,25 @@ def _segments(work: dict | None, num_seqs: int):
 
 
 def block_gates(u: torch.Tensor, wa_t: torch.Tensor, ba: torch.Tensor | None, wb_t: torch.Tensor, bb: torch.Tensor | None,
-                softplus_rate: torch.Tensor, c_r: float, a: torch.Tensor, b: torch.Tensor) -> None:
+                softplus_rate: torch.Tensor, c_r: float, a: torch.Tensor, b: torch.Tensor,
+                bf16_weights: tuple | None = None) -> None:
     """What the gated recurrence multiplies and adds at every token: r = sigmoid(A_b u_b + ba), g = sigmoid(B_b u_b + bb)
     per block b of the channels, then a = exp(c_r * r * softplus_rate) and b = sqrt(1 - a^2) * g * u.  wa_t, wb_t float32
-    [blocks, in, out]; u, a, b float32 [T, C]."""
+    [blocks, in, out]; u, a, b float32 [T, C].  ``bf16_weights`` = (A, B) as bfloat16 [blocks, out, in]: the two products
+    run on the tensor cores with u rounded to bfloat16 for them (a bfloat16 run's way with its projections), where the
+    blocks' width is a multiple of 16 up to 256; everything behind the products stays float."""
     _need_cuda(u, wa_t, wb_t, a, b)
     T, C = u.shape
     if any(t.dtype != torch.float32 or not t.is_contiguous() for t in (u, wa_t, wb_t, a, b, softplus_rate)):
         raise KernelError("block_gates: contiguous float32 tensors are wanted")
+    bw = C // wa_t.shape[0]
+    if bf16_weights is not None and bw % 16 == 0 and bw <= 256:
+        wa, wb = bf16_weights
+        if wa.dtype != torch.bfloat16 or wb.dtype != torch.bfloat16 or not wa.is_contiguous() or not wb.is_contiguous():
+            raise KernelError("block_gates: contiguous bfloat16 weights [blocks, out, in] are wanted")
+        _check(library().acv_block_gates_mma(_p(u), _p(wa), _p(ba), _p(wb), _p(bb), _p(softplus_rate), float(c_r), _p(a),
+                                             _p(b), T, C, wa.shape[0], _stream()), "block_gates")
+        return
     _check(library().acv_block_gates(_p(u), _p(wa_t), _p(ba), _p(wb_t), _p(bb), _p(softplus_rate), float(c_r), _p(a), _p(b),
                                      T, C, wa_t.shape[0], _stream()), "block_gates")
 

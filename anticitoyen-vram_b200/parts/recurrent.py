@@ -129,7 +129,8 @@ class GatedLinearRecurrence(SegmentedRecurrence):
         out = W_o (S * y)
 
     What a request keeps: the last ``conv`` - 1 inputs of the convolution and S, both float32.  Gates, decays and the
-    recurrence are 32-bit in every run precision; the two input projections leave their product as float32.
+    recurrence are 32-bit in every run precision; the two input projections leave their product as float32, and in
+    bfloat16 runs the gates' projections take u rounded to bfloat16 (with float accumulation).
     Tensors behind ``prefix``: y, y.b, x, x.b, conv, conv.b, ra, ra.b, ri, ri.b, lam, o."""
 
     NAMES = {n: n for n in ("y", "y.b", "x", "x.b", "conv", "conv.b", "ra", "ra.b", "ri", "ri.b", "lam", "o")}
@@ -173,6 +174,8 @@ class GatedLinearRecurrence(SegmentedRecurrence):
         # [blocks, out, in] -> [blocks, in, out]: the threads of a warp then read neighbouring outputs
         self.wa_t, self.wb_t = f("ra").transpose(1, 2).contiguous(), f("ri").transpose(1, 2).contiguous()
         self.ba, self.bb = f("ra.b").reshape(-1).contiguous(), f("ri.b").reshape(-1).contiguous()
+        # a bfloat16 run makes the two gate projections on the tensor cores, from the weights as the file has them
+        self.gate_weights = (w("ra").contiguous(), w("ri").contiguous()) if rt.dtype == torch.bfloat16 else None
         # softplus of the decay parameter is a constant of the weights: folded once, in float64
         lam = tensors[self._n("lam")].to(torch.float64)
         self.softplus_lam = torch.nn.functional.softplus(lam).to(device=rt.device, dtype=torch.float32).contiguous()
@@ -201,7 +204,8 @@ class GatedLinearRecurrence(SegmentedRecurrence):
         ops.causal_conv(xy[:, :C], self.x_bias, self.conv_w, self.conv_b, conv_state, conv_slots, ctx.cu_q,
                         ctx.seq_of_token, u)
         a, b = torch.empty_like(u), torch.empty_like(u)
-        ops.block_gates(u, self.wa_t, self.ba, self.wb_t, self.bb, self.softplus_lam, -self.rate, a, b)
+        ops.block_gates(u, self.wa_t, self.ba, self.wb_t, self.bb, self.softplus_lam, -self.rate, a, b,
+                        bf16_weights=self.gate_weights)
         st = cache.parts["state"]
         mixed = torch.empty((T, C), device=h.device, dtype=h.dtype)
         ops.gated_scan(a, b, xy[:, C:], self.y_bias, st.state, ctx.state_slots[st.group], ctx.cu_q, ctx.num_seqs, mixed,

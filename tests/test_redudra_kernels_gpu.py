@@ -365,3 +365,25 @@ def test_tensor_core_product_adds_its_bias(M, N, K):
     out = torch.empty(M, N // 2, device=DEV, dtype=torch.bfloat16)
     ops.gemm_tc(x, w, out, swiglu_pairs=True, bias=bias)
     close(out, paired.double().cpu().numpy(), 2e-2, "paired")
+
+
+@pytest.mark.parametrize("T", [1, 64, 200])
+@pytest.mark.parametrize("C,blocks", [(512, 2), (96, 3), (128, 8), (2048, 16)])
+def test_gates_on_the_tensor_cores_equal_the_float_ones(C, blocks, T):
+    """With inputs and weights that bfloat16 holds exactly the two forms compute the same sums (every product of two
+    bfloat16 numbers is exact in float): they may differ by the order of the additions alone."""
+    from acvram_b200.kernels import ops
+    g = torch.Generator().manual_seed(C + T)
+    bw = C // blocks
+    u = torch.randn(T, C, generator=g).to(torch.bfloat16)
+    wa = (torch.randn(blocks, bw, bw, generator=g) / math.sqrt(bw)).to(torch.bfloat16)
+    wb = (torch.randn(blocks, bw, bw, generator=g) / math.sqrt(bw)).to(torch.bfloat16)
+    ba, bb = torch.randn(C, generator=g).to(DEV), torch.randn(C, generator=g).to(DEV)
+    sp = torch.rand(C, generator=g).to(DEV) * 0.7
+    ud = u.float().to(DEV)
+    wa_t, wb_t = wa.float().transpose(1, 2).contiguous().to(DEV), wb.float().transpose(1, 2).contiguous().to(DEV)
+    a0, b0, a1, b1 = (torch.empty(T, C, device=DEV) for _ in range(4))
+    ops.block_gates(ud, wa_t, ba, wb_t, bb, sp, -8.0, a0, b0)
+    ops.block_gates(ud, wa_t, ba, wb_t, bb, sp, -8.0, a1, b1, bf16_weights=(wa.to(DEV), wb.to(DEV)))
+    close(a1, a0.double().cpu().numpy(), 2e-5, "a")
+    close(b1, b0.double().cpu().numpy(), 2e-5, "b")
