@@ -171,13 +171,25 @@ __global__ void __launch_bounds__(128) block_gates_mma_kernel(const float* __res
     const int LD = BW + 8;                                      // elements of a padded row
     bf16* As = reinterpret_cast<bf16*>(gm_smem);                // [64][LD]
     bf16* Bs = As + 64 * LD;                                    // [2][64][LD]
+    float* cs = reinterpret_cast<float*>(Bs + 2 * 64 * LD);     // [3][64]: the two biases and the rate of the tile's outputs
     pdl_launch_dependents();
     pdl_wait();
     const int t0 = blockIdx.x * 64, blk = blockIdx.y, o0 = blockIdx.z * 64;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    for (int i = tid; i < 64 * BW; i += 128) {
-        const int tt = i / BW, e = i - tt * BW;
-        As[tt * LD + e] = __float2bfloat16_rn(t0 + tt < T ? u[(size_t)(t0 + tt) * C + blk * BW + e] : 0.f);
+    const int quads = BW / 4;                                   // 16-byte pieces of a row of u
+#pragma unroll 4
+    for (int i = tid; i < 64 * quads; i += 128) {
+        const int tt = i / quads, e = (i - tt * quads) * 4;
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (t0 + tt < T) v = *reinterpret_cast<const float4*>(u + (size_t)(t0 + tt) * C + blk * BW + e);
+        *reinterpret_cast<uint2*>(As + tt * LD + e) = make_uint2(pack_bf16(v.x, v.y), pack_bf16(v.z, v.w));
+    }
+    if (tid < 64) {
+        const int ch = blk * BW + o0 + tid;
+        const bool in = o0 + tid < BW;
+        cs[tid] = in && ba ? ba[ch] : 0.f;
+        cs[64 + tid] = in && bb ? bb[ch] : 0.f;
+        cs[128 + tid] = in ? c_r * sp[ch] : 0.f;
     }
     const int chunks = BW / 8;                                  // 16-byte pieces of a weight row
     for (int i = tid; i < 2 * 64 * chunks; i += 128) {
@@ -212,19 +224,35 @@ __global__ void __launch_bounds__(128) block_gates_mma_kernel(const float* __res
                 mma_bf16(acc[q][j], a, *reinterpret_cast<const uint32_t*>(b_row), *reinterpret_cast<const uint32_t*>(b_row + 8));
             }
     }
+    // the unrounded inputs of this thread's outputs: all loads first, so that they do not wait for one another
+    float2 uu[8][2];
 #pragma unroll
     for (int j = 0; j < 8; ++j)
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-            const int t = t0 + warp * 16 + gr + (e >> 1) * 8;
-            const int o = o0 + j * 8 + 2 * tq + (e & 1);
-            if (t < T && o < BW) {
-                const int ch = blk * BW + o;
-                const float rr = 1.f / (1.f + expf(-(acc[0][j][e] + (ba ? ba[ch] : 0.f))));
-                const float gg = 1.f / (1.f + expf(-(acc[1][j][e] + (bb ? bb[ch] : 0.f))));
-                const float la = c_r * sp[ch] * rr;
-                r[(size_t)t * C + ch] = expf(la);
-                g[(size_t)t * C + ch] = sqrtf(fmaxf(-expm1f(2.f * la), 0.f)) * gg * u[(size_t)t * C + ch];
+        for (int hh = 0; hh < 2; ++hh) {
+            const int t = t0 + warp * 16 + gr + hh * 8, o = o0 + j * 8 + 2 * tq;
+            uu[j][hh] = t < T && o < BW ? *reinterpret_cast<const float2*>(u + (size_t)t * C + blk * BW + o) : make_float2(0.f, 0.f);
+        }
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {
+            const int t = t0 + warp * 16 + gr + hh * 8;
+            const int ol = j * 8 + 2 * tq;                      // the first of this thread's two neighbouring outputs
+            if (t < T && o0 + ol < BW) {
+                float av[2], bv[2];
+#pragma unroll
+                for (int x = 0; x < 2; ++x) {
+                    const int e = hh * 2 + x;
+                    const float rr = 1.f / (1.f + expf(-(acc[0][j][e] + cs[ol + x])));
+                    const float gg = 1.f / (1.f + expf(-(acc[1][j][e] + cs[64 + ol + x])));
+                    const float la = cs[128 + ol + x] * rr;
+                    av[x] = expf(la);
+                    bv[x] = sqrtf(fmaxf(-expm1f(2.f * la), 0.f)) * gg * (x ? uu[j][hh].y : uu[j][hh].x);
+                }
+                const size_t at = (size_t)t * C + blk * BW + o0 + ol;
+                *reinterpret_cast<float2*>(r + at) = make_float2(av[0], av[1]);
+                *reinterpret_cast<float2*>(g + at) = make_float2(bv[0], bv[1]);
             }
         }
 }
@@ -236,8 +264,8 @@ ACV_API int acv_block_gates_mma(const float* u, const void* wa, const float* ba,
     if (blocks <= 0 || C % blocks) return ACV_ERR_SIZE;
     const int BW = C / blocks;
     if (BW % 16 || BW > 256) return ACV_ERR_SIZE;
-    if (((uintptr_t)wa & 15) || ((uintptr_t)wb & 15)) return ACV_ERR_ALIGN;
-    const int smem = 3 * 64 * (BW + 8) * 2;
+    if (((uintptr_t)wa & 15) || ((uintptr_t)wb & 15) || ((uintptr_t)u & 15) || ((uintptr_t)r & 7) || ((uintptr_t)g & 7)) return ACV_ERR_ALIGN;
+    const int smem = 3 * 64 * (BW + 8) * 2 + 3 * 64 * 4;
     static AcvSmemConfig cfg;
     if (smem > 48 * 1024) {
         const int e = acv_ensure_smem(cfg, block_gates_mma_kernel, smem);
