@@ -160,8 +160,10 @@ ACV_API int acv_block_gates(const float* u, const float* wa, const float* ba, co
 
 // The same on the tensor cores, for runs whose projections are bfloat16: the inputs u are rounded to bfloat16 for the
 // two products (float accumulation); sigmoid, decay and b stay float and b takes the unrounded u.  wa, wb: bfloat16
-// [blocks][out][in] as the weight file has them.  grid (tiles of 64 tokens, blocks, tiles of 64 outputs), four warps
-// of 16 tokens; the tile of u and the weights' 2 x 64 rows wait in shared memory with rows padded by 16 bytes.
+// [blocks][out][in] as the weight file has them.  grid (tiles of 64 tokens, blocks, tiles of OT outputs), four warps
+// of 16 tokens; the tile of u and the weights' 2 x OT rows wait in shared memory with rows padded by 16 bytes.  OT is 64,
+// or 16 for steps of few tokens, whose grid would otherwise be a few blocks that each wait for 2 x 64 rows of weights.
+template <int OT>
 __global__ void __launch_bounds__(128) block_gates_mma_kernel(const float* __restrict__ u, const bf16* __restrict__ wa,
                                                              const float* __restrict__ ba, const bf16* __restrict__ wb,
                                                              const float* __restrict__ bb, const float* __restrict__ sp,
@@ -170,11 +172,11 @@ __global__ void __launch_bounds__(128) block_gates_mma_kernel(const float* __res
     extern __shared__ __align__(16) unsigned char gm_smem[];
     const int LD = BW + 8;                                      // elements of a padded row
     bf16* As = reinterpret_cast<bf16*>(gm_smem);                // [64][LD]
-    bf16* Bs = As + 64 * LD;                                    // [2][64][LD]
-    float* cs = reinterpret_cast<float*>(Bs + 2 * 64 * LD);     // [3][64]: the two biases and the rate of the tile's outputs
+    bf16* Bs = As + 64 * LD;                                    // [2][OT][LD]
+    float* cs = reinterpret_cast<float*>(Bs + 2 * OT * LD);     // [3][OT]: the two biases and the rate of the tile's outputs
     pdl_launch_dependents();
     pdl_wait();
-    const int t0 = blockIdx.x * 64, blk = blockIdx.y, o0 = blockIdx.z * 64;
+    const int t0 = blockIdx.x * 64, blk = blockIdx.y, o0 = blockIdx.z * OT;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int quads = BW / 4;                                   // 16-byte pieces of a row of u
 #pragma unroll 4
@@ -184,29 +186,30 @@ __global__ void __launch_bounds__(128) block_gates_mma_kernel(const float* __res
         if (t0 + tt < T) v = *reinterpret_cast<const float4*>(u + (size_t)(t0 + tt) * C + blk * BW + e);
         *reinterpret_cast<uint2*>(As + tt * LD + e) = make_uint2(pack_bf16(v.x, v.y), pack_bf16(v.z, v.w));
     }
-    if (tid < 64) {
+    if (tid < OT) {
         const int ch = blk * BW + o0 + tid;
         const bool in = o0 + tid < BW;
         cs[tid] = in && ba ? ba[ch] : 0.f;
-        cs[64 + tid] = in && bb ? bb[ch] : 0.f;
-        cs[128 + tid] = in ? c_r * sp[ch] : 0.f;
+        cs[OT + tid] = in && bb ? bb[ch] : 0.f;
+        cs[2 * OT + tid] = in ? c_r * sp[ch] : 0.f;
     }
     const int chunks = BW / 8;                                  // 16-byte pieces of a weight row
-    for (int i = tid; i < 2 * 64 * chunks; i += 128) {
-        const int q = i / (64 * chunks), rem = i - q * 64 * chunks;
+    for (int i = tid; i < 2 * OT * chunks; i += 128) {
+        const int q = i / (OT * chunks), rem = i - q * OT * chunks;
         const int row = rem / chunks, ch = rem - row * chunks;
         uint4 v = make_uint4(0, 0, 0, 0);
         if (o0 + row < BW)
             v = *reinterpret_cast<const uint4*>((q ? wb : wa) + ((size_t)blk * BW + o0 + row) * BW + ch * 8);
-        *reinterpret_cast<uint4*>(Bs + ((size_t)q * 64 + row) * LD + ch * 8) = v;
+        *reinterpret_cast<uint4*>(Bs + ((size_t)q * OT + row) * LD + ch * 8) = v;
     }
     __syncthreads();
     const int gr = lane >> 2, tq = lane & 3;
-    float acc[2][8][4];
+    constexpr int NT = OT / 8;                                  // output tiles of eight
+    float acc[2][NT][4];
 #pragma unroll
     for (int q = 0; q < 2; ++q)
 #pragma unroll
-        for (int j = 0; j < 8; ++j)
+        for (int j = 0; j < NT; ++j)
 #pragma unroll
             for (int e = 0; e < 4; ++e) acc[q][j][e] = 0.f;
     const bf16* a_row = As + (warp * 16 + gr) * LD + 2 * tq;
@@ -219,22 +222,22 @@ __global__ void __launch_bounds__(128) block_gates_mma_kernel(const float* __res
 #pragma unroll
         for (int q = 0; q < 2; ++q)
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                const bf16* b_row = Bs + ((size_t)q * 64 + j * 8 + gr) * LD + k0 + 2 * tq;
+            for (int j = 0; j < NT; ++j) {
+                const bf16* b_row = Bs + ((size_t)q * OT + j * 8 + gr) * LD + k0 + 2 * tq;
                 mma_bf16(acc[q][j], a, *reinterpret_cast<const uint32_t*>(b_row), *reinterpret_cast<const uint32_t*>(b_row + 8));
             }
     }
     // the unrounded inputs of this thread's outputs: all loads first, so that they do not wait for one another
-    float2 uu[8][2];
+    float2 uu[NT][2];
 #pragma unroll
-    for (int j = 0; j < 8; ++j)
+    for (int j = 0; j < NT; ++j)
 #pragma unroll
         for (int hh = 0; hh < 2; ++hh) {
             const int t = t0 + warp * 16 + gr + hh * 8, o = o0 + j * 8 + 2 * tq;
             uu[j][hh] = t < T && o < BW ? *reinterpret_cast<const float2*>(u + (size_t)t * C + blk * BW + o) : make_float2(0.f, 0.f);
         }
 #pragma unroll
-    for (int j = 0; j < 8; ++j)
+    for (int j = 0; j < NT; ++j)
 #pragma unroll
         for (int hh = 0; hh < 2; ++hh) {
             const int t = t0 + warp * 16 + gr + hh * 8;
@@ -245,8 +248,8 @@ __global__ void __launch_bounds__(128) block_gates_mma_kernel(const float* __res
                 for (int x = 0; x < 2; ++x) {
                     const int e = hh * 2 + x;
                     const float rr = 1.f / (1.f + expf(-(acc[0][j][e] + cs[ol + x])));
-                    const float gg = 1.f / (1.f + expf(-(acc[1][j][e] + cs[64 + ol + x])));
-                    const float la = cs[128 + ol + x] * rr;
+                    const float gg = 1.f / (1.f + expf(-(acc[1][j][e] + cs[OT + ol + x])));
+                    const float la = cs[2 * OT + ol + x] * rr;
                     av[x] = expf(la);
                     bv[x] = sqrtf(fmaxf(-expm1f(2.f * la), 0.f)) * gg * (x ? uu[j][hh].y : uu[j][hh].x);
                 }
@@ -265,15 +268,21 @@ ACV_API int acv_block_gates_mma(const float* u, const void* wa, const float* ba,
     const int BW = C / blocks;
     if (BW % 16 || BW > 256) return ACV_ERR_SIZE;
     if (((uintptr_t)wa & 15) || ((uintptr_t)wb & 15) || ((uintptr_t)u & 15) || ((uintptr_t)r & 7) || ((uintptr_t)g & 7)) return ACV_ERR_ALIGN;
-    const int smem = 3 * 64 * (BW + 8) * 2 + 3 * 64 * 4;
-    static AcvSmemConfig cfg;
+    const int ot = T <= 128 ? 16 : 64;
+    const int smem = (64 + 2 * ot) * (BW + 8) * 2 + 3 * ot * 4;
+    static AcvSmemConfig cfg64, cfg16;
     if (smem > 48 * 1024) {
-        const int e = acv_ensure_smem(cfg, block_gates_mma_kernel, smem);
+        const int e = ot == 64 ? acv_ensure_smem(cfg64, block_gates_mma_kernel<64>, smem)
+                               : acv_ensure_smem(cfg16, block_gates_mma_kernel<16>, smem);
         if (e) return e;
     }
-    dim3 grid((T + 63) / 64, blocks, (BW + 63) / 64);
-    acv_launch(PDL_MISC, block_gates_mma_kernel, grid, 128, smem, stream, u, (const bf16*)wa, ba, (const bf16*)wb, bb, sp, c_r,
-               r, g, T, C, BW);
+    dim3 grid((T + 63) / 64, blocks, (BW + ot - 1) / ot);
+    if (ot == 64)
+        acv_launch(PDL_MISC, block_gates_mma_kernel<64>, grid, 128, smem, stream, u, (const bf16*)wa, ba, (const bf16*)wb, bb,
+                   sp, c_r, r, g, T, C, BW);
+    else
+        acv_launch(PDL_MISC, block_gates_mma_kernel<16>, grid, 128, smem, stream, u, (const bf16*)wa, ba, (const bf16*)wb, bb,
+                   sp, c_r, r, g, T, C, BW);
     return acv_launch_status();
 }
 

@@ -257,7 +257,106 @@ def moe_case(tokens: int, reps: int, H: int = 4096, E: int = 64, top: int = 6, F
             "weights_gbs_gate_up": chosen * 2 * F * H * 2 / us_up / 1e3, "weights_gbs_down": chosen * F * H * 2 / us_dn / 1e3}
 
 
+# ----------------------------------------------------------------------------- the kernels of the state-keeping mixers
+def _steps(q_len: int, batch: int):
+    """cu_q, seq_of_token, positions, slots and the segment items of ``batch`` requests that bring ``q_len`` tokens each."""
+    dev = "cuda"
+    cu = torch.arange(batch + 1, device=dev, dtype=torch.int32) * q_len
+    seq_of = torch.arange(batch, device=dev, dtype=torch.int32).repeat_interleave(q_len)
+    pos = torch.arange(q_len, device=dev, dtype=torch.int32).repeat(batch)
+    slots = torch.arange(batch, device=dev, dtype=torch.int32)
+    arrays, values = ops.segment_work([q_len] * batch)
+    work = {**{k: torch.from_numpy(v).to(dev) for k, v in arrays.items()}, **values}
+    return cu, seq_of, pos, slots, work
+
+
+def retention_case(q_len: int, batch: int, reps: int, H: int = 16, D: int = 64, DV: int = 128) -> dict:
+    """Retention of ``batch`` requests that bring ``q_len`` tokens each: 16 heads of 64 x 128, rotary over the whole key."""
+    dev = "cuda"
+    T = q_len * batch
+    cu, _, pos, slots, work = _steps(q_len, batch)
+    proj = torch.randn(T, H * (2 * D + 2 * DV), device=dev, dtype=torch.bfloat16)
+    table = torch.rand(max(q_len, 2), D, device=dev)
+    decay = torch.full((H,), 0.97, device=dev)
+    state = torch.zeros(batch, H, D, DV, device=dev)
+    o = torch.empty(T, H * DV, device=dev)
+    out = torch.empty(T, H * DV, device=dev, dtype=torch.bfloat16)
+    a, b = H * D, 2 * H * D
+    fn = lambda i: ops.retention(proj[:, :a], proj[:, a:b], proj[:, b:b + H * DV], table, pos, decay, D ** -0.5, state, slots,
+                                 cu, batch, o, H, D, DV, work=work)
+    us = _time(fn, reps)
+    us_gate = _time(lambda i: ops.retention_gate(o, proj[:, b + H * DV:], out, H, DV, 1e-6, 0.5), reps)
+    flops = 4.0 * T * H * D * DV * (1.5 if work["summaries"] else 1.0)
+    nbytes = 2 * state.numel() * 4 + T * H * (2 * D + DV) * 2 + o.numel() * 4
+    print(f"retention q_len={q_len} batch={batch} heads={H} of {D}x{DV}: {us:.1f} us ({flops / us / 1e6:.2f} TFLOP/s float, "
+          f"{nbytes / us / 1e3:.0f} GB/s), gate {us_gate:.1f} us")
+    return {"kernel": "retention", "q_len": q_len, "batch": batch, "us": us, "us_gate": us_gate, "tflops": flops / us / 1e6,
+            "gbs": nbytes / us / 1e3}
+
+
+def recurrence_case(q_len: int, batch: int, reps: int, C: int = 4096, blocks: int = 16, taps: int = 4) -> dict:
+    """The gated linear recurrence's kernels for ``batch`` requests of ``q_len`` tokens: 4096 channels in 16 blocks."""
+    dev = "cuda"
+    T = q_len * batch
+    bw = C // blocks
+    cu, seq_of, _, slots, work = _steps(q_len, batch)
+    xy = torch.randn(T, 2 * C, device=dev)
+    bias = torch.zeros(C, device=dev)
+    taps_w = torch.randn(C, taps, device=dev)
+    conv_state = torch.zeros(batch, taps - 1, C, device=dev)
+    u, a, b = (torch.empty(T, C, device=dev) for _ in range(3))
+    wa = (torch.randn(blocks, bw, bw, device=dev) / bw ** 0.5).to(torch.bfloat16)
+    wb = (torch.randn(blocks, bw, bw, device=dev) / bw ** 0.5).to(torch.bfloat16)
+    wa_t, wb_t = wa.float().transpose(1, 2).contiguous(), wb.float().transpose(1, 2).contiguous()
+    sp = torch.rand(C, device=dev)
+    state = torch.zeros(batch, C, device=dev)
+    out = torch.empty(T, C, device=dev, dtype=torch.bfloat16)
+    us_conv = _time(lambda i: ops.causal_conv(xy[:, :C], bias, taps_w, bias, conv_state, slots, cu, seq_of, u), reps)
+    us_mma = _time(lambda i: ops.block_gates(u, wa_t, bias, wb_t, bias, sp, -8.0, a, b, bf16_weights=(wa, wb)), reps)
+    us_ffma = _time(lambda i: ops.block_gates(u, wa_t, bias, wb_t, bias, sp, -8.0, a, b), reps)
+    us_scan = _time(lambda i: ops.gated_scan(a, b, xy[:, C:], bias, state, slots, cu, batch, out, work=work), reps)
+    gflop = 4.0 * T * C * bw / 1e9
+    print(f"recurrence q_len={q_len} batch={batch} channels={C} in {blocks} blocks: conv {us_conv:.1f} us "
+          f"({T * C * 12 / us_conv / 1e3:.0f} GB/s), gates mma.sync {us_mma:.1f} us ({gflop / us_mma * 1e3:.1f} TFLOP/s) / FFMA "
+          f"{us_ffma:.1f} us ({gflop / us_ffma * 1e3:.1f} TFLOP/s), scan {us_scan:.1f} us ({T * C * 14 / us_scan / 1e3:.0f} GB/s)")
+    return {"kernel": "recurrence", "q_len": q_len, "batch": batch, "us_conv": us_conv, "us_gates_mma": us_mma,
+            "us_gates_ffma": us_ffma, "us_scan": us_scan}
+
+
+def norm_shift_case(q_len: int, batch: int, reps: int, H: int = 4096) -> dict:
+    """Residual sum + layer norm + token shift over a float stream of width 4096."""
+    dev = "cuda"
+    T = q_len * batch
+    cu, seq_of, _, slots, _ = _steps(q_len, batch)
+    x = torch.randn(T, H, device=dev)
+    delta = torch.randn(T, H, device=dev, dtype=torch.bfloat16) * 0.01
+    w, b, mu = torch.ones(H, device=dev), torch.zeros(H, device=dev), torch.rand(H, device=dev)
+    state = torch.zeros(batch, H, device=dev)
+    n, out = torch.empty(T, H, device=dev), torch.empty(T, H, device=dev, dtype=torch.bfloat16)
+
+    def two(i):
+        ops.add_layernorm(x, delta, w, b, 1e-6, n, None, 0.5)
+        ops.token_shift(n, mu, state, slots, cu, seq_of, out)
+
+    us = _time(two, reps)
+    nbytes = T * H * (4 + 4 + 2 + 2) + T * H * 8 * 2
+    line = f"layer norm + token shift T={T} width={H}: two launches {us:.1f} us ({nbytes / us / 1e3:.0f} GB/s)"
+    res = {"kernel": "layernorm_shift", "T": T, "us_two": us}
+    if q_len == 1:
+        us1 = _time(lambda i: ops.add_layernorm_shift(x, delta, w, b, 1e-6, mu, state, slots, out, 0.5), reps)
+        line += f", one launch {us1:.1f} us ({T * H * 12 / us1 / 1e3:.0f} GB/s)"
+        res["us_one"] = us1
+    print(line)
+    return res
+
+
 CASES = {
+    "retention_prefill": lambda r: retention_case(2048, 1, r),
+    "retention_decode_b64": lambda r: retention_case(1, 64, r),
+    "recurrence_prefill": lambda r: recurrence_case(2048, 1, r),
+    "recurrence_decode_b64": lambda r: recurrence_case(1, 64, r),
+    "norm_shift_prefill": lambda r: norm_shift_case(2048, 1, r),
+    "norm_shift_decode_b64": lambda r: norm_shift_case(1, 64, r),
     "moe_decode_b64": lambda r: moe_case(64, r),
     "moe_decode_b8": lambda r: moe_case(8, r),
     "moe_prefill": lambda r: moe_case(2048, r),
