@@ -7,7 +7,8 @@
 // multiplied by k_scale, all in float, as they are staged; scores, state and sums are 32-bit.  A second kernel
 // brings each head's o to unit RMS (no weight), multiplies by silu(gate) and a constant, and rounds once.
 //
-// acv_retention: grid (items, heads).  The block's threads are G groups of DV: thread (g, c) keeps rows
+// acv_retention: grid (items, heads, tiles of DVT value columns: the columns of S do not know of one another, and a
+// head too wide for one block's threads is cut).  The block's threads are G groups of DVT: thread (g, c) keeps rows
 // g*R .. g*R+R-1 of column c of S in registers (R as large as the registers allow, up to 64: a thread that holds a
 // whole column needs no other thread for its sums, and a block of DV threads leaves room for several blocks on an SM), walks its tokens in chunks of TC (q, k, v staged in shared memory,
 // the partial sums of the chunk reduced over the groups afterwards), and writes S back.
@@ -38,12 +39,12 @@ __global__ void __launch_bounds__(ret_max_threads(R)) retention_kernel(const T* 
                                  const int* __restrict__ positions, const float* __restrict__ decay, float k_scale,
                                  float* __restrict__ state, const int* __restrict__ slots,
                                  const int* __restrict__ cu_q, RetSegments sg, float* __restrict__ o, int ldo, int H, int D, int DV,
-                                 int G, int TC) {
+                                 int G, int TC, int DVT) {
     extern __shared__ float sm[];
     float* qs = sm;                         // [TC][D]
     float* ks = qs + (size_t)TC * D;        // [TC][D]
-    float* vs = ks + (size_t)TC * D;        // [TC][DV]
-    float* red = vs + (size_t)TC * DV;      // [TC][G][DV]
+    float* vs = ks + (size_t)TC * D;        // [TC][DVT]
+    float* red = vs + (size_t)TC * DVT;     // [TC][G][DVT]
     pdl_launch_dependents();
     pdl_wait();
     const int item = blockIdx.x, h = blockIdx.y;
@@ -54,8 +55,9 @@ __global__ void __launch_bounds__(ret_max_threads(R)) retention_kernel(const T* 
     const bool last = t1 == q1;
     if (SUMMARY && last) return;
     const int tid = threadIdx.x, nthr = blockDim.x;
-    const int c = tid % DV, g = tid / DV;
-    const bool owner = g < G;
+    const int cl = tid % DVT, g = tid / DVT, c0 = blockIdx.z * DVT;
+    const int c = c0 + cl;                  // this thread's column of S
+    const bool owner = g < G && c < DV;
     const float dec = decay[h];
     const size_t HS = (size_t)D * DV;
     float* st = state + ((size_t)slots[seq] * H + h) * HS;
@@ -90,9 +92,9 @@ __global__ void __launch_bounds__(ret_max_threads(R)) retention_kernel(const T* 
             qs[i] = to_f32(q[at]);
             ks[i] = to_f32(k[at]) * k_scale;
         }
-        for (int i = tid; i < n * DV; i += nthr) {
-            const int tt = i / DV, e = i - tt * DV;
-            vs[i] = to_f32(v[(size_t)(tb + tt) * ld + (size_t)h * DV + e]);
+        for (int i = tid; i < n * DVT; i += nthr) {
+            const int tt = i / DVT, e = i - tt * DVT;
+            vs[i] = c0 + e < DV ? to_f32(v[(size_t)(tb + tt) * ld + (size_t)h * DV + c0 + e]) : 0.f;
         }
         __syncthreads();
         if (cos_sin) {
@@ -115,7 +117,7 @@ __global__ void __launch_bounds__(ret_max_threads(R)) retention_kernel(const T* 
         }
         if (owner) {
             for (int tt = 0; tt < n; ++tt) {
-                const float vv = vs[tt * DV + c];
+                const float vv = vs[tt * DVT + cl];
                 const float* kr = ks + tt * D + g * R;
                 const float* qr = qs + tt * D + g * R;
                 float part = 0.f;
@@ -126,16 +128,17 @@ __global__ void __launch_bounds__(ret_max_threads(R)) retention_kernel(const T* 
                         if (!SUMMARY) part = fmaf(S[i], qr[i], part);
                     }
                 }
-                if (!SUMMARY) red[((size_t)tt * G + g) * DV + c] = part;
+                if (!SUMMARY) red[((size_t)tt * G + g) * DVT + cl] = part;
             }
         }
         __syncthreads();
         if (!SUMMARY) {
-            for (int i = tid; i < n * DV; i += nthr) {
-                const int tt = i / DV, e = i - tt * DV;
+            for (int i = tid; i < n * DVT; i += nthr) {
+                const int tt = i / DVT, e = i - tt * DVT;
+                if (c0 + e >= DV) continue;
                 float sum = 0.f;
-                for (int gg = 0; gg < G; ++gg) sum += red[((size_t)tt * G + gg) * DV + e];
-                o[(size_t)(tb + tt) * ldo + (size_t)h * DV + e] = sum;
+                for (int gg = 0; gg < G; ++gg) sum += red[((size_t)tt * G + gg) * DVT + e];
+                o[(size_t)(tb + tt) * ldo + (size_t)h * DV + c0 + e] = sum;
             }
         }
         // the next chunk's staging writes qs, ks, vs only; its first barrier stands between this read of red and the
@@ -187,10 +190,11 @@ template <typename T, int R>
 static int launch_retention(const void* q, const void* k, const void* v, int ld, const float* cos_sin, int rot,
                             int table_rows, const int* positions, const float* decay, float k_scale, float* state,
                             const int* slots, const int* cu_q, RetSegments sg, int summaries, float* o, int ldo, int num_seqs, int H, int D, int DV,
-                            cudaStream_t stream) {
+                            int DVT, cudaStream_t stream) {
     const int G = (D + R - 1) / R;
-    const int threads = ((G * DV + 31) / 32) * 32;
-    const size_t per_token = (size_t)(2 * D + DV + G * DV) * sizeof(float);
+    const int threads = ((G * DVT + 31) / 32) * 32;
+    const size_t per_token = (size_t)(2 * D + DVT + G * DVT) * sizeof(float);
+    const dim3 grid(num_seqs, H, (DV + DVT - 1) / DVT);
     int TC = (int)((48 * 1024) / per_token);
     TC = TC > 32 ? 32 : TC;
     if (TC < 1) TC = 1;
@@ -203,12 +207,12 @@ static int launch_retention(const void* q, const void* k, const void* v, int ld,
         if (e) return e;
     }
     if (summaries) {
-        acv_launch(PDL_ATTN, retention_kernel<T, R, true>, dim3(num_seqs, H), threads, smem, stream, (const T*)q, (const T*)k,
-                   (const T*)v, ld, cos_sin, rot, table_rows, positions, decay, k_scale, state, slots, cu_q, sg, o, ldo, H, D, DV, G, TC);
+        acv_launch(PDL_ATTN, retention_kernel<T, R, true>, grid, threads, smem, stream, (const T*)q, (const T*)k,
+                   (const T*)v, ld, cos_sin, rot, table_rows, positions, decay, k_scale, state, slots, cu_q, sg, o, ldo, H, D, DV, G, TC, DVT);
         acv_launch(PDL_ATTN, retention_fold_kernel, dim3(num_seqs, H, (D * DV + 255) / 256), 256, 0, stream, sg, cu_q, decay, H, D * DV);
     }
-    acv_launch(PDL_ATTN, retention_kernel<T, R, false>, dim3(num_seqs, H), threads, smem, stream, (const T*)q, (const T*)k,
-               (const T*)v, ld, cos_sin, rot, table_rows, positions, decay, k_scale, state, slots, cu_q, sg, o, ldo, H, D, DV, G, TC);
+    acv_launch(PDL_ATTN, retention_kernel<T, R, false>, grid, threads, smem, stream, (const T*)q, (const T*)k,
+               (const T*)v, ld, cos_sin, rot, table_rows, positions, decay, k_scale, state, slots, cu_q, sg, o, ldo, H, D, DV, G, TC, DVT);
     return acv_launch_status();
 }
 
@@ -216,11 +220,11 @@ template <typename T>
 static int retention_by_rows(int R, const void* q, const void* k, const void* v, int ld, const float* cos_sin, int rot,
                              int table_rows, const int* positions, const float* decay, float k_scale, float* state,
                              const int* slots, const int* cu_q, RetSegments sg, int summaries, float* o, int ldo, int num_seqs, int H, int D, int DV,
-                             cudaStream_t stream) {
+                             int DVT, cudaStream_t stream) {
 #define RET_CASE(N)                                                                                                  \
     case N:                                                                                                          \
         return launch_retention<T, N>(q, k, v, ld, cos_sin, rot, table_rows, positions, decay, k_scale, state, slots, \
-                                      cu_q, sg, summaries, o, ldo, num_seqs, H, D, DV, stream);
+                                      cu_q, sg, summaries, o, ldo, num_seqs, H, D, DV, DVT, stream);
     switch (R) {
         RET_CASE(4) RET_CASE(8) RET_CASE(16) RET_CASE(32) RET_CASE(64)
     }
@@ -239,28 +243,37 @@ ACV_API int acv_retention(const void* q, const void* k, const void* v, int ld, c
                           int dtype, cudaStream_t stream) {
     const int num_seqs = n_items;
     if (num_seqs <= 0) return 0;
-    if (H <= 0 || D <= 0 || DV <= 0 || DV > 1024 || (cos_sin && (rot <= 0 || rot > D || (rot & 1)))) return ACV_ERR_SIZE;
+    if (H <= 0 || D <= 0 || DV <= 0 || (cos_sin && (rot <= 0 || rot > D || (rot & 1)))) return ACV_ERR_SIZE;
     if (seg_len <= 0 || (summaries && (!seg_seq || !seg_idx || !seg_state))) return ACV_ERR_SIZE;
     RetSegments sg;
     sg.seq = seg_seq; sg.idx = seg_idx; sg.len = seg_len; sg.state = seg_state;
     // rows of the state that a thread keeps: the fewest that let the block fit `want` threads (measured on a B200 at
     // 64 x 128 per head: blocks of 1024, 512 and 128 threads, see the design notes); ACVRAM_RETENTION_ROWS forces a choice
     static const int forced = getenv("ACVRAM_RETENTION_ROWS") ? atoi(getenv("ACVRAM_RETENTION_ROWS")) : 0;
-    int R = 4;
-    while (R <= 64 && ((D + R - 1) / R) * DV > (ret_max_threads(R) < RET_WANT_THREADS ? ret_max_threads(R) : RET_WANT_THREADS)) R *= 2;
-    if (R > 64) {       // no such block: the most threads that the registers allow
-        R = 4;
-        while (R <= 64 && ((D + R - 1) / R) * DV > ret_max_threads(R)) R *= 2;
+    auto rows_for = [&](int dvt, int want) {        // the fewest rows with which G groups of dvt threads fit `want`, 0: none
+        for (int r = 4; r <= 64; r *= 2) {
+            const int most = ret_max_threads(r) < want ? ret_max_threads(r) : want;
+            if (((D + r - 1) / r) * dvt <= most) return r;
+        }
+        return 0;
+    };
+    // a head whose columns do not fit one block is cut into tiles of columns (each a block of its own)
+    int DVT = DV, R = 0;
+    while (true) {
+        R = rows_for(DVT, RET_WANT_THREADS);
+        if (!R) R = rows_for(DVT, 1024);
+        if (R || DVT <= 32) break;
+        DVT = DVT > 128 ? 128 : DVT / 2;
     }
     if (forced == 4 || forced == 8 || forced == 16 || forced == 32 || forced == 64)
-        if (((D + forced - 1) / forced) * DV <= ret_max_threads(forced)) R = forced;
-    if (R > 64) return ACV_ERR_SIZE;      // (a state of more than 64 x 256 elements per head is not built)
+        if (((D + forced - 1) / forced) * DVT <= ret_max_threads(forced)) R = forced;
+    if (!R) return ACV_ERR_SIZE;          // (key rows of more than 512 elements are not built)
     if (dtype == ACV_F32)
         return retention_by_rows<float>(R, q, k, v, ld, cos_sin, rot, table_rows, positions, decay, k_scale, state, slots,
-                                        cu_q, sg, summaries, o, ldo, num_seqs, H, D, DV, stream);
+                                        cu_q, sg, summaries, o, ldo, num_seqs, H, D, DV, DVT, stream);
     if (dtype == ACV_BF16)
         return retention_by_rows<bf16>(R, q, k, v, ld, cos_sin, rot, table_rows, positions, decay, k_scale, state, slots,
-                                       cu_q, sg, summaries, o, ldo, num_seqs, H, D, DV, stream);
+                                       cu_q, sg, summaries, o, ldo, num_seqs, H, D, DV, DVT, stream);
     return ACV_ERR_DTYPE;
 }
 

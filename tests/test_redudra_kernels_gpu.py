@@ -208,7 +208,8 @@ def test_gates_and_scan_over_steps(C, blocks):
 
 # --------------------------------------------------------------------------- retention
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("H,D,DV,rot", [(3, 8, 16, 8), (1, 32, 32, 0), (5, 12, 20, 12), (2, 64, 80, 32), (2, 128, 128, 64), (1, 256, 64, 0)])
+@pytest.mark.parametrize("H,D,DV,rot", [(3, 8, 16, 8), (1, 32, 32, 0), (5, 12, 20, 12), (2, 64, 80, 32), (2, 128, 128, 64), (1, 256, 64, 0),
+                                          (2, 96, 192, 32), (1, 128, 256, 0), (1, 48, 300, 16)])     # heads too wide for one block's threads
 def test_retention_over_steps(H, D, DV, rot, dtype):
     from acvram_b200.kernels import ops
     rng = np.random.default_rng(D + DV)
