@@ -831,6 +831,10 @@ def attention(qkv: torch.Tensor, out: torch.Tensor, k_pages: torch.Tensor, v_pag
     keep_first = keep_first if window > 0 else 0
     w = work if work is not None else ctx.work
     generic = value_dim != head_dim or not tensor_core_attention_takes(qkv.dtype, num_heads, num_kv_heads, head_dim)
+    # the tensor-core kernels read queries in 16-byte pieces: a view into a wider projection whose rows or start are not
+    # aligned so (a mixer beside another one, with sizes that are multiples of nothing) takes the generic kernel
+    if not generic and (qkv.stride(0) % 8 or qkv.data_ptr() % 16):
+        generic = True
     # kept first keys: the split-KV decode kernel and the tcgen05 portion kernel know them, the mma.sync portion kernel does not
     if not generic and keep_first > 0 and (chunk > 0 or (w["n_tiles"] and not attention_tc_takes(qkv, out, k_pages, head_dim))):
         generic = True

@@ -53,7 +53,8 @@ def config(which: str) -> dict:
     C: sizes that are multiples of nothing (width 100, dim 24, vdim 40, 3 heads), a window of 7 (less than a page) that
        keeps 9 (more than the window), five taps, five blocks, the last layer alone looped twice.
     D: sizes that the tensor-core kernels take (dim = vdim = 64 and 128, width 128), windows of 48 and 80 keeping 4 and 16,
-       the middle layer looped twice."""
+       the middle layer looped twice.
+    E: see below."""
     if which == "A":
         layers = [parallel(left(4, 2, 16, 24, 20, 3, rot(5000.0, 8, (3.0, 64, 8.0, 1.0))), right(3, 8, 16, (0.9, 0.97, 0.995), rot(300.0, 8)), 0.7, 0.4, 80),
                   rglru(64, 2, 3, 0),
@@ -73,6 +74,11 @@ def config(which: str) -> dict:
                   rglru(128, 4, 4, 160),
                   parallel(left(2, 1, 128, 128, 80, 16, rot(20000.0, 64)), right(2, 32, 64, (0.9, 0.99), rot(1000.0, 32)), 0.8, 0.3, 0)]
         return _model(320, 128, layers, 1e-6, 0.5, 30.0, (1, 2, 2))
+    if which == "E":      # an attention of the tensor-core kernels' sizes beside a retention whose sizes leave the
+        # stacked projection's rows unaligned (358 elements) and the output projection's inputs odd (149)
+        layers = [parallel(left(2, 1, 64, 64, 40, 2, rot(900.0, 32)), right(3, 10, 7, (0.9, 0.95, 0.99), rot(70.0, 10)), 0.9, 1.1, 56),
+                  rglru(48, 3, 2, 0)]
+        return _model(131, 72, layers, 1e-5, 0.7, 0.0, (0, 1, 2))
     raise KeyError(which)
 
 

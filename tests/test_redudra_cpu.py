@@ -21,7 +21,7 @@ from acvram_b200.parts import Runtime
 from acvram_b200.parts.position import Rotary
 
 
-@pytest.mark.parametrize("which", ["A", "B", "C", "D"])
+@pytest.mark.parametrize("which", ["A", "B", "C", "D", "E"])
 def test_config_round_trip_plan_and_schedule(which):
     raw = ru.config(which)
     cfg = RedudraConfig.from_dict(raw)

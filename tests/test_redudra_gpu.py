@@ -31,7 +31,7 @@ BF16_MEDIAN, BF16_WORST = 0.03, 0.15     # bfloat16: the median position and the
 @pytest.fixture(scope="module")
 def folders(tmp_path_factory):
     root = tmp_path_factory.mktemp("redudra")
-    return {w: ru.write_model(str(root / w), ru.config(w), seed=23 + i) for i, w in enumerate("ABCD")}
+    return {w: ru.write_model(str(root / w), ru.config(w), seed=23 + i) for i, w in enumerate("ABCDE")}
 
 
 @functools.lru_cache(maxsize=None)
@@ -97,7 +97,7 @@ def judge(folder, requests, got, dtype, what=""):
 
 # --------------------------------------------------------------------------- whole prompts, layer by layer
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("which", ["A", "B", "C", "D"])
+@pytest.mark.parametrize("which", ["A", "B", "C", "D", "E"])
 def test_whole_prompts(folders, which, dtype):
     f = folders[which]
     runner = make_runner(f, dtype)
@@ -128,7 +128,7 @@ def test_stream_after_every_layer_run(folders, which):
 
 # --------------------------------------------------------------------------- prefill against decoding, portions
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("which", ["A", "B", "C", "D"])
+@pytest.mark.parametrize("which", ["A", "B", "C", "D", "E"])
 def test_decoding_token_by_token(folders, which, dtype):
     """A prompt, then 120 tokens one by one: over page borders (16) and past every window (7 to 80) and its kept first
     tokens; in bfloat16 through captured graphs.  A second request decodes from its second token on."""
@@ -190,7 +190,7 @@ def mixed_schedule(requests: dict, seed: int, max_live: int):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("which", ["A", "B", "C", "D"])
+@pytest.mark.parametrize("which", ["A", "B", "C", "D", "E"])
 def test_mixed_batches_in_a_small_pool(folders, which, dtype):
     """Seven unequal requests, three live at a time, portions beside single tokens, with rows of the block tables, pages
     and state slots for three requests: all are used again (the states of a slot's former request must be gone), and
