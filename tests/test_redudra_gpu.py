@@ -295,3 +295,23 @@ def test_trace_run_program(folders, tmp_path):
     b = np.fromfile(out / "2.f32", dtype="<f4").reshape(-1, vocab)
     assert float(ru.row_errors(a, full[[0, 29]]).max()) < F32_BOUND
     assert float(ru.row_errors(b, np.stack([full[44], full[6]])).max()) < F32_BOUND
+
+
+@pytest.mark.parametrize("ahead", [False, True])
+def test_preemption_starts_the_states_anew(folders, ahead):
+    """B keeps all keys of its last layer, so a pool of 7 pages cannot hold three requests of 55 tokens: requests are
+    preempted and computed again from their first token, in state slots that others have used meanwhile.  Their states
+    must start at zero again: the greedy tokens stay the oracle's."""
+    from acvram_b200 import Engine, SamplingParams
+    f = folders["B"]
+    cfg, tensors = _read(f)
+    prompts = [list(ids_of(f, n, 500 + n)) for n in (20, 25, 18)]
+    want = [pr.greedy(cfg, tensors, p, 30) for p in prompts]
+    engine = Engine(f, "float32", max_batch_size=3, max_model_len=128, page_size=16, num_pages=7, token_budget=16,
+                    device="cuda:0", run_ahead=ahead)
+    got = engine.generate_batch(prompts, SamplingParams(temperature=0.0, max_tokens=30, ignore_eos=True))
+    assert not engine.stats.failed_steps, engine.last_error
+    assert engine.stats.preempted > 0, "the pool was meant to be too small"
+    assert got == want
+    engine.runner.manager.check()
+    assert all(g.num_free == g.max_requests for g in engine.runner.manager.state_groups)
