@@ -306,9 +306,9 @@ ZOTONEX_SIZES = {
 REDUDRA_SIZES = {
     # width; attention: heads, kv heads, head size (keys and values), window, kept first tokens; retention: heads, key size,
     # value size; recurrence: channels, blocks, taps; feed-forward size
-    "s": dict(width=2048, heads=16, kv_heads=4, dim=128, window=1024, keep=4, r_heads=8, r_dim=64, r_vdim=128,
+    "s": dict(width=2048, heads=16, kv_heads=4, dim=128, window=1024, keep=8, r_heads=8, r_dim=64, r_vdim=128,
               channels=2048, blocks=16, taps=4, ff=6144),
-    "m": dict(width=4096, heads=32, kv_heads=8, dim=128, window=2048, keep=4, r_heads=16, r_dim=64, r_vdim=128,
+    "m": dict(width=4096, heads=32, kv_heads=8, dim=128, window=2048, keep=8, r_heads=16, r_dim=64, r_vdim=128,
               channels=4096, blocks=16, taps=4, ff=12288),
 }
 
@@ -337,15 +337,15 @@ def run_redudra(args) -> int:
         par = {"type": "parallel", "mlp": {"kind": "dense", "ff": z["ff"]}, "mixer": {
             "left": {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["dim"], "scale": z["dim"] ** -0.5,
                      "mask": {"size": z["window"], "keep_first": z["keep"]},
-                     "rot": {"base": 1e6, "dims": z["dim"], "scaling": {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}}},
+                     "rot": {"base": 1e6, "dims": z["dim"], "scaling": {"factor": 8.0, "original": 4096, "fast": 16.0, "slow": 2.0}}},
             "right": {"heads": z["r_heads"], "dim": z["r_dim"], "vdim": z["r_vdim"],
                       "decay": [1.0 - 2.0 ** (-5 - 3 * h / z["r_heads"]) for h in range(z["r_heads"])],
                       "rot": {"base": 1e4, "dims": z["r_dim"]}},
-            "left_scale": 0.6, "right_scale": 0.5}}
+            "left_scale": 0.7, "right_scale": 0.4}}
         rec = {"type": "rglru", "mlp": {"kind": "dense", "ff": z["ff"]},
                "mixer": {"width": z["channels"], "blocks": z["blocks"], "conv": z["taps"]}}
         rcfg = RedudraConfig.from_dict({"architecture": "Redudra", "vocab": vocab, "width": z["width"], "norm": {"eps": 1e-6},
-                                        "residual_mult": 0.5, "logit_softcap": 30.0,
+                                        "residual_mult": 0.4, "logit_softcap": 50.0,
                                         "layers": [par if i % 2 == 0 else rec for i in range(layers)]})
         qcfg = Qwen3Config(vocab_size=vocab, hidden_size=z["width"], intermediate_size=z["ff"], num_hidden_layers=layers,
                            num_attention_heads=z["heads"], num_key_value_heads=z["kv_heads"], head_dim=z["dim"],

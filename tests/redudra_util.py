@@ -70,10 +70,10 @@ def config(which: str) -> dict:
                   rglru(100, 5, 5, 36)]
         return _model(157, 100, layers, 1e-5, 0.6, 12.0, (1, 2, 2))
     if which == "D":
-        layers = [parallel(left(4, 2, 64, 64, 48, 4, rot(20000.0, 64, (4.0, 128, 16.0, 1.0))), right(2, 64, 64, (0.97, 0.995), rot(1000.0, 64)), 0.6, 0.5, 160),
+        layers = [parallel(left(4, 2, 64, 64, 48, 4, rot(30000.0, 64, (3.0, 128, 16.0, 1.0))), right(2, 64, 64, (0.97, 0.995), rot(1000.0, 64)), 0.65, 0.45, 160),
                   rglru(128, 4, 4, 160),
-                  parallel(left(2, 1, 128, 128, 80, 16, rot(20000.0, 64)), right(2, 32, 64, (0.9, 0.99), rot(1000.0, 32)), 0.8, 0.3, 0)]
-        return _model(320, 128, layers, 1e-6, 0.5, 30.0, (1, 2, 2))
+                  parallel(left(2, 1, 128, 128, 80, 16, rot(30000.0, 64)), right(2, 32, 64, (0.9, 0.99), rot(1000.0, 32)), 0.8, 0.3, 0)]
+        return _model(320, 128, layers, 1e-6, 0.5, 28.0, (1, 2, 2))
     if which == "E":      # an attention of the tensor-core kernels' sizes beside a retention whose sizes leave the
         # stacked projection's rows unaligned (358 elements) and the output projection's inputs odd (149)
         layers = [parallel(left(2, 1, 64, 64, 40, 2, rot(900.0, 32)), right(3, 10, 7, (0.9, 0.95, 0.99), rot(70.0, 10)), 0.9, 1.1, 56),

@@ -122,7 +122,7 @@ def test_state_slots_come_back_and_go_out_again():
     m.check()
 
 
-@pytest.mark.parametrize("rot", [ru.rot(5000.0, 8, (3.0, 64, 8.0, 1.0)), ru.rot(20000.0, 64, (4.0, 128, 16.0, 1.0)),
+@pytest.mark.parametrize("rot", [ru.rot(5000.0, 8, (3.0, 64, 8.0, 1.0)), ru.rot(30000.0, 64, (3.0, 128, 16.0, 1.0)),
                                  ru.rot(777.0, 10, (2.5, 40, 4.0, 0.5)), ru.rot(300.0, 16)])
 def test_rotary_table_has_the_oracles_frequencies(rot):
     sc = rot.get("scaling")

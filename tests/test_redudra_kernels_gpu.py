@@ -285,7 +285,7 @@ class Paged:
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("NH,NKV,D,DV,rot,window,keep,page,n", [
     (4, 2, 16, 24, 8, 20, 3, 16, 200), (2, 2, 32, 32, 32, 24, 0, 16, 200), (3, 3, 24, 40, 10, 7, 9, 8, 200),
-    (6, 1, 64, 80, 64, 136, 4, 16, 200), (2, 1, 64, 64, 64, 48, 4, 16, 200), (2, 2, 16, 16, 16, 0, 0, 16, 200),
+    (6, 2, 64, 80, 48, 120, 5, 16, 200), (2, 1, 64, 64, 64, 48, 4, 16, 200), (2, 2, 16, 16, 16, 0, 0, 16, 200),
     (4, 2, 128, 128, 64, 100, 140, 64, 700), (2, 2, 64, 64, 32, 130, 1, 32, 450)])
 def test_rope_append_and_attention_with_planted_keys(NH, NKV, D, DV, rot, window, keep, page, n, dtype):
     """Keys are planted so that, for the last query, one key far back would win the softmax by a wide margin if it were
