@@ -83,7 +83,7 @@ def play(runner, requests: dict, steps) -> dict:
     return {r: torch.cat(v).numpy() for r, v in rows.items()}
 
 
-def judge(folder, requests, got, dtype, what=""):
+def agree(folder, requests, got, dtype, what=""):
     for r, ids in requests.items():
         err = ru.row_errors(got[r], oracle(folder, tuple(ids)))
         assert np.isfinite(err).all(), f"{what} {r}: not finite"
@@ -103,7 +103,7 @@ def test_whole_prompts(folders, which, dtype):
     runner = make_runner(f, dtype)
     requests = {f"w{n}": ids_of(f, n, n) for n in (1, 2, 23, 150, 333)}     # the first tokens alone; page and window borders
     got = play(runner, requests, [{r: len(ids)} for r, ids in requests.items()])
-    judge(f, requests, got, dtype, "whole")
+    agree(f, requests, got, dtype, "whole")
 
 
 @pytest.mark.parametrize("which", ["A", "C"])
@@ -137,7 +137,7 @@ def test_decoding_token_by_token(folders, which, dtype):
     requests = {"d": ids_of(f, 37 + 120, 21), "e": ids_of(f, 1 + 30, 22)}
     steps = [{"d": 37}] + [{"d": 1}] * 120 + [{"e": 1}] * 31
     got = play(runner, requests, steps)
-    judge(f, requests, got, dtype, "decode")
+    agree(f, requests, got, dtype, "decode")
     if dtype == "bfloat16":
         assert runner.graph_launches > 0, "the decode steps did not replay a captured graph"
 
@@ -151,7 +151,7 @@ def test_portions_of_any_size(folders, which, dtype):
     sizes = [2, 3, 2, 17, 5, 31, 2, 40, 7, 64, 2, 16, 1, 1, 1]
     sizes.append(len(ids) - sum(sizes))
     got = play(runner, {"p": ids}, [{"p": n} for n in sizes])
-    judge(f, {"p": ids}, got, dtype, "portions")
+    agree(f, {"p": ids}, got, dtype, "portions")
 
 
 def test_long_decoding_in_few_pages(folders):
@@ -162,7 +162,7 @@ def test_long_decoding_in_few_pages(folders):
     runner = make_runner(f, "float32", pages=14, page_size=8, max_requests=2)
     ids = ids_of(f, 500, 77)
     got = play(runner, {"long": ids}, [{"long": 30}, {"long": 11}, {"long": 2}, {"long": 30}, {"long": 27}] + [{"long": 1}] * 400)
-    judge(f, {"long": ids}, got, "float32", "long")
+    agree(f, {"long": ids}, got, "float32", "long")
 
 
 # --------------------------------------------------------------------------- batches, pages and slots used again
@@ -201,7 +201,7 @@ def test_mixed_batches_in_a_small_pool(folders, which, dtype):
     pages = 3 * (-(-160 // 16))
     runner = make_runner(f, dtype, pages=pages, max_requests=3, graphs=dtype == "bfloat16")
     got = play(runner, requests, mixed_schedule(requests, 7, 3))
-    judge(f, requests, got, dtype, "mixed")
+    agree(f, requests, got, dtype, "mixed")
     assert all(g.pool.num_free == pages for g in runner.manager.paged_groups)
     assert all(g.num_free == 3 for g in runner.manager.state_groups)
 
@@ -215,7 +215,7 @@ def test_a_far_key_decides(folders, dtype):
     ids = ids_of(f, 640, 99)
     runner = make_runner(f, dtype, pages=48)
     got = play(runner, {"far": ids}, [{"far": 590}] + [{"far": 1}] * 50)
-    judge(f, {"far": ids}, got, dtype, "far")
+    agree(f, {"far": ids}, got, dtype, "far")
     cut = oracle(f, tuple(ids[48:]))                   # the same tokens without the first three pages
     err = ru.row_errors(cut[-40:], oracle(f, ids)[-40:])
     assert float(np.median(err)) > 2 * BF16_MEDIAN, "the far keys do not matter in this test: it shows nothing"
