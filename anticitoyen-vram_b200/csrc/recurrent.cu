@@ -62,13 +62,69 @@ __global__ void causal_conv_kernel(const T* __restrict__ x, int ldx, const float
     }
 }
 
+// The same for float inputs with four neighbouring channels to a thread (16-byte loads and stores): C and the row
+// stride multiples of four, x, the state and u aligned to 16 bytes.  wt: the taps transposed, [K][C], so that the four
+// channels' taps of one lag are one vector as well.
+__device__ __forceinline__ float4 f4_add(float4 a, float4 b) { return make_float4(a.x + b.x, a.y + b.y, a.z + b.z, a.w + b.w); }
+__device__ __forceinline__ float4 f4_fma(float4 w, float4 v, float4 acc) {
+    return make_float4(fmaf(w.x, v.x, acc.x), fmaf(w.y, v.y, acc.y), fmaf(w.z, v.z, acc.z), fmaf(w.w, v.w, acc.w));
+}
+
+__global__ void causal_conv4_kernel(const float* __restrict__ x, int ldx, const float* __restrict__ xb,
+                                    const float* __restrict__ wt, const float* __restrict__ cb, float* __restrict__ state,
+                                    const int* __restrict__ slots, const int* __restrict__ cu_q,
+                                    const int* __restrict__ seq_of_token, float* __restrict__ u, int C, int K) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t = blockIdx.x;
+    const int c = (blockIdx.y * blockDim.x + threadIdx.x) * 4;
+    if (c >= C) return;
+    const int seq = seq_of_token[t];
+    const int first = cu_q[seq], len = cu_q[seq + 1] - first;
+    const int off = t - first;
+    const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
+    const float4 bias_in = xb ? *reinterpret_cast<const float4*>(xb + c) : zero;
+    const float4 bias_out = cb ? *reinterpret_cast<const float4*>(cb + c) : zero;
+    auto tap = [&](int j) { return *reinterpret_cast<const float4*>(wt + (size_t)j * C + c); };     // the j-th tap of the four channels
+    auto in = [&](int row) { return f4_add(*reinterpret_cast<const float4*>(x + (size_t)row * ldx + c), bias_in); };
+    if (off >= K - 1) {
+        float4 acc = bias_out;
+        for (int j = 0; j < K; ++j) acc = f4_fma(tap(K - 1 - j), in(t - j), acc);
+        *reinterpret_cast<float4*>(u + (size_t)t * C + c) = acc;
+        return;
+    }
+    if (off != 0) return;
+    float* st = state + (size_t)slots[seq] * (K - 1) * C;      // [K-1][C], the oldest input first
+    const int n_here = len < K - 1 ? len : K - 1;
+    for (int n = 0; n < n_here; ++n) {
+        float4 acc = bias_out;
+        for (int j = 0; j < K; ++j) {
+            const int src = n - j;
+            const float4 v = src >= 0 ? in(first + src) : *reinterpret_cast<const float4*>(st + (size_t)(K - 1 + src) * C + c);
+            acc = f4_fma(tap(K - 1 - j), v, acc);
+        }
+        *reinterpret_cast<float4*>(u + (size_t)(first + n) * C + c) = acc;
+    }
+    for (int i = 0; i < K - 1; ++i) {       // ascending: what is read lies behind what has been written
+        const int src = len - (K - 1) + i;
+        const float4 v = src >= 0 ? in(first + src) : *reinterpret_cast<const float4*>(st + (size_t)(len + i) * C + c);
+        *reinterpret_cast<float4*>(st + (size_t)i * C + c) = v;
+    }
+}
+
+// w: the taps [C][K]; wt (may be null): the same transposed, [K][C], which the form with four channels to a thread reads
 ACV_API int acv_causal_conv(const void* x, int ldx, const float* xb, const float* w, const float* cb, float* state,
                             const int* slots, const int* cu_q, const int* seq_of_token, float* u, int T, int C, int K,
-                            int dtype, cudaStream_t stream) {
+                            int dtype, const float* wt, cudaStream_t stream) {
     if (T <= 0) return 0;
     if (C <= 0 || K < 1) return ACV_ERR_SIZE;
     dim3 grid(T, (C + 127) / 128);
-    if (dtype == ACV_F32)
+    const bool four = wt && !((uintptr_t)wt & 15) && dtype == ACV_F32 && C % 4 == 0 && ldx % 4 == 0 && !((uintptr_t)x & 15) && !((uintptr_t)u & 15) &&
+                      !((uintptr_t)state & 15) && (!xb || !((uintptr_t)xb & 15)) && (!cb || !((uintptr_t)cb & 15));
+    if (four)
+        acv_launch(PDL_MISC, causal_conv4_kernel, dim3(T, (C / 4 + 127) / 128), 128, 0, stream, (const float*)x, ldx, xb, wt, cb,
+                   state, slots, cu_q, seq_of_token, u, C, K);
+    else if (dtype == ACV_F32)
         acv_launch(PDL_MISC, causal_conv_kernel<float>, grid, 128, 0, stream, (const float*)x, ldx, xb, w, cb, state, slots,
                    cu_q, seq_of_token, u, C, K);
     else if (dtype == ACV_BF16)

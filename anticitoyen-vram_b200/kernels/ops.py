@@ -76,7 +76,7 @@ def _declare(lib: ctypes.CDLL) -> None:
         "acv_add_layernorm_shift": [P, P, F, P, P, P, P, P, P, I, I, F, I, I, P],
         "acv_add_row_f32": [P, P, I, I, P],
         "acv_softcap_f32": [P, LL, F, P],
-        "acv_causal_conv": [P, I, P, P, P, P, P, P, P, P, I, I, I, I, P],
+        "acv_causal_conv": [P, I, P, P, P, P, P, P, P, P, I, I, I, I, P, P],
         "acv_block_gates": [P, P, P, P, P, P, F, P, P, I, I, I, P],
         "acv_block_gates_mma": [P, P, P, P, P, P, F, P, P, I, I, I, P],
         "acv_gated_scan": [P, P, P, I, P, P, P, P, P, P, I, P, I, P, I, I, I, I, I, P],
@@ -1312,17 +1312,20 @@ def softcap_f32(x: torch.Tensor, cap: float) -> torch.Tensor:
 # ----------------------------------------------------------------------------- gated linear recurrence
 def causal_conv(x: torch.Tensor, x_bias: torch.Tensor | None, taps: torch.Tensor, conv_bias: torch.Tensor | None,
                 state: torch.Tensor, slots: torch.Tensor, cu_q: torch.Tensor, seq_of_token: torch.Tensor,
-                out: torch.Tensor) -> torch.Tensor:
+                out: torch.Tensor, taps_t: torch.Tensor | None = None) -> torch.Tensor:
     """out[t, c] = conv_bias[c] + sum_j taps[c, K-1-j] * (x[t-j, c] + x_bias[c]) over each request's tokens; what lies
     before the step comes from ``state`` (float32 [slots, K-1, C], oldest first), which is replaced.  x: [T, C] view
-    (row stride free), out float32 [T, C]."""
+    (row stride free), out float32 [T, C].  ``taps_t``: the taps transposed ([K, C], float32): float inputs with aligned
+    rows then take the kernel that gives a thread four neighbouring channels."""
     _need_cuda(x, taps, state, out)
     T, C = out.shape
     K = taps.shape[1]
     if out.dtype != torch.float32 or not out.is_contiguous() or x.stride(1) != 1 or taps.dtype != torch.float32 or not state.is_contiguous():
         raise KernelError("causal_conv: float32 taps, state and output are wanted")
     _check(library().acv_causal_conv(_p(x), x.stride(0), _p(x_bias), _p(taps), _p(conv_bias), _p(state), _p(slots), _p(cu_q),
-                                     _p(seq_of_token), _p(out), T, C, K, dtype_code(x.dtype), _stream()), "causal_conv")
+                                     _p(seq_of_token), _p(out), T, C, K, dtype_code(x.dtype),
+                                     _p(taps_t) if taps_t is not None and taps_t.is_contiguous() and taps_t.shape == (K, C) else None,
+                                     _stream()), "causal_conv")
     return out
 
 

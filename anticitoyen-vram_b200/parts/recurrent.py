@@ -171,6 +171,7 @@ class GatedLinearRecurrence(SegmentedRecurrence):
         self.o = Linear(w("o"))
         self.x_bias, self.y_bias = f("x.b"), f("y.b")
         self.conv_w, self.conv_b = f("conv"), f("conv.b")
+        self.conv_w_t = self.conv_w.t().contiguous()         # [taps, channels]: four channels' taps of a lag are one vector
         # [blocks, out, in] -> [blocks, in, out]: the threads of a warp then read neighbouring outputs
         self.wa_t, self.wb_t = f("ra").transpose(1, 2).contiguous(), f("ri").transpose(1, 2).contiguous()
         self.ba, self.bb = f("ra.b").reshape(-1).contiguous(), f("ri.b").reshape(-1).contiguous()
@@ -202,7 +203,7 @@ class GatedLinearRecurrence(SegmentedRecurrence):
         else:
             conv_state, conv_slots = u, ctx.state_slots[cache.parts["state"].group]      # never read: no tap reaches back
         ops.causal_conv(xy[:, :C], self.x_bias, self.conv_w, self.conv_b, conv_state, conv_slots, ctx.cu_q,
-                        ctx.seq_of_token, u)
+                        ctx.seq_of_token, u, taps_t=self.conv_w_t)
         a, b = torch.empty_like(u), torch.empty_like(u)
         ops.block_gates(u, self.wa_t, self.ba, self.wb_t, self.bb, self.softplus_lam, -self.rate, a, b,
                         bf16_weights=self.gate_weights)

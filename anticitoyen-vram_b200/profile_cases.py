@@ -311,7 +311,8 @@ def recurrence_case(q_len: int, batch: int, reps: int, C: int = 4096, blocks: in
     sp = torch.rand(C, device=dev)
     state = torch.zeros(batch, C, device=dev)
     out = torch.empty(T, C, device=dev, dtype=torch.bfloat16)
-    us_conv = _time(lambda i: ops.causal_conv(xy[:, :C], bias, taps_w, bias, conv_state, slots, cu, seq_of, u), reps)
+    taps_t = taps_w.t().contiguous()
+    us_conv = _time(lambda i: ops.causal_conv(xy[:, :C], bias, taps_w, bias, conv_state, slots, cu, seq_of, u, taps_t=taps_t), reps)
     us_mma = _time(lambda i: ops.block_gates(u, wa_t, bias, wb_t, bias, sp, -8.0, a, b, bf16_weights=(wa, wb)), reps)
     us_ffma = _time(lambda i: ops.block_gates(u, wa_t, bias, wb_t, bias, sp, -8.0, a, b), reps)
     us_scan = _time(lambda i: ops.gated_scan(a, b, xy[:, C:], bias, state, slots, cu, batch, out, work=work), reps)

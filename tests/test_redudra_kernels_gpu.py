@@ -133,7 +133,7 @@ def test_layernorm_of_chosen_rows_leaves_the_stream():
 def test_causal_conv_over_steps(taps):
     from acvram_b200.kernels import ops
     rng = np.random.default_rng(taps)
-    C = 70
+    C = 72
     lengths = [9, 9, 4]
     xs = [bf(rng.standard_normal((n, C))) for n in lengths]
     xb, w, cb = bf(0.1 * rng.standard_normal(C)), bf(rng.standard_normal((C, taps))), bf(0.1 * rng.standard_normal(C))
@@ -148,7 +148,15 @@ def test_causal_conv_over_steps(taps):
             wide = torch.zeros((x.shape[0], C + 10), device=DEV, dtype=torch.bfloat16)      # a view with a row stride of its own
             wide[:, 3:3 + C] = x
             out = torch.empty((x.shape[0], C), device=DEV)
-            ops.causal_conv(wide[:, 3:3 + C], dev(xb), dev(w), dev(cb), state, i32([slots[r] for r, _, _ in step]), cu, seq_of, out)
+            sl = i32([slots[r] for r, _, _ in step])
+            # float inputs in a view whose rows and start are aligned take the form with four channels to a thread;
+            # it works on a copy of the state and must leave the same outputs and the same state
+            wide32 = torch.zeros((x.shape[0], 2 * C), device=DEV)
+            wide32[:, :C] = x.float()
+            state32, out32 = state.clone(), torch.empty_like(out)
+            ops.causal_conv(wide32[:, :C], dev(xb), dev(w), dev(cb), state32, sl, cu, seq_of, out32, taps_t=dev(w.T.copy()))
+            ops.causal_conv(wide[:, 3:3 + C], dev(xb), dev(w), dev(cb), state, sl, cu, seq_of, out)
+            assert torch.equal(out32, out) and torch.equal(state32, state)
             o = 0
             for r, a, c in step:
                 got[r][a:a + c] = out[o:o + c].cpu().numpy()
